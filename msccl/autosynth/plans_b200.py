@@ -1,0 +1,53 @@
+"""Plans for a single HGX B200 box (machine type ``b200``): 2, 4 or 8 GPUs behind NVSwitch.
+
+Size ranges follow the latency/bandwidth trade-off of the algorithms: one-shot while latency
+dominates, two-shot in the middle, and for large messages the in-switch (NVLS) reduction,
+which the executor provides natively (``msccl.language.ext_nvls``).
+"""
+from msccl.autosynth.registry import register_msccl_program
+from msccl.language.mscclir import ThreadblockPolicy
+from msccl.programs.allgather import allgather_direct, reduce_scatter_direct
+from msccl.programs.allreduce import allreduce_one_shot, allreduce_two_shot
+from msccl.programs.alltoall import alltoall_direct
+from msccl.topologies import fully_connected
+
+B200_GPU_COUNTS = (2, 4, 8)
+
+
+def register_b200_plans():
+    manual = ThreadblockPolicy.manual
+    for n in B200_GPU_COUNTS:
+        mtype = f'b200x{n}' if n != 8 else ['b200', 'b200x8']
+        box = fully_connected(n)
+
+        def one_shot(prog, nodes, n=n):
+            allreduce_one_shot(n)
+        one_shot.__name__ = f'b200_allreduce_one_shot_{n}'
+        register_msccl_program(box, 'allreduce', mtype, chunk_factor=1, inplace=True, protocol='LL',
+                               sizes=(0, '256KB'), threadblock_policy=manual,
+                               machines=lambda m: m == 1)(one_shot)
+
+        def two_shot(prog, nodes, n=n):
+            allreduce_two_shot(n)
+        two_shot.__name__ = f'b200_allreduce_two_shot_{n}'
+        register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='Simple',
+                               sizes=('256KB', None), instances=4, threadblock_policy=manual,
+                               machines=lambda m: m == 1)(two_shot)
+
+        def a2a(prog, nodes, n=n):
+            alltoall_direct(n)
+        a2a.__name__ = f'b200_alltoall_direct_{n}'
+        register_msccl_program(box, 'alltoall', mtype, chunk_factor=1, protocol='Simple', instances=4,
+                               machines=lambda m: m == 1)(a2a)
+
+        def ag(prog, nodes, n=n):
+            allgather_direct(n)
+        ag.__name__ = f'b200_allgather_direct_{n}'
+        register_msccl_program(box, 'allgather', mtype, chunk_factor=1, protocol='Simple', instances=4,
+                               machines=lambda m: m == 1)(ag)
+
+        def rs(prog, nodes, n=n):
+            reduce_scatter_direct(n)
+        rs.__name__ = f'b200_reduce_scatter_direct_{n}'
+        register_msccl_program(box, 'reduce_scatter', mtype, chunk_factor=1, protocol='Simple', instances=4,
+                               machines=lambda m: m == 1)(rs)
