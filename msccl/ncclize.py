@@ -99,6 +99,13 @@ def _liveness(gpus, algorithm):
     live = {rank: {'i': [[(-1, -1)] for _ in range(g.input_chunks)],
                    'o': [[(math.inf, math.inf)] for _ in range(g.output_chunks)],
                    's': [[(math.inf, -1)] for _ in g.scratch]} for rank, g in gpus.items()}
+    for rank, g in gpus.items():
+        # An address that is both input and output stays in its input slot and is copied to the
+        # output after the last step, so that slot is occupied for the whole algorithm.  (The
+        # reference omits this and can remap scratch on top of data the final copy still needs.)
+        for addr, idx in g.inputs.items():
+            if addr in g.outputs:
+                live[rank]['i'][idx][0] = (-1, math.inf)
     for t, step in enumerate(algorithm.steps):
         for addr, src, dst in step.sends:
             for rank in (src, dst):
@@ -366,16 +373,39 @@ def ncclize(algorithm, remap_scratch=None, channel_policy=ChannelPolicy.MatchTop
                 readers_since[(rank, cp.src_buffer, cp.src_offset + i)].append(cp)
                 last_writers[(rank, cp.dst_buffer, cp.dst_offset + i)].append(cp)
 
+    combining = algorithm.collective.is_combining
+    chunked = algorithm.collective.chunk_up(algorithm.instance.chunks)
+    content = {rank: defaultdict(frozenset) for rank in gpus}
+    for c in chunked.chunks():
+        for rank in chunked.ranks():
+            if chunked.precondition(rank, c):
+                content[rank][chunked.address(c)] = content[rank][chunked.address(c)] | {c}
     xml_step = 0
     for algo_step in algorithm.steps:
-        # serialise multiple arrivals at one destination slot into sub-steps
+        # Serialise multiple arrivals at one destination slot into sub-steps and decide whether
+        # an arrival overwrites ('r') or is added ('rrc').  ``content`` tracks which chunks of the
+        # collective each (rank, address) currently holds: an arrival that already contains what
+        # the slot holds replaces it (the all-gather half of an all-reduce), an arrival with
+        # disjoint content is reduced into it.  (The reference reduces whenever the slot was
+        # written before, which double counts in composed all-reduces.)
+        sent_content = {(addr, src): content[src].get(addr, frozenset()) for addr, src, _dst in algo_step.sends}
         arrivals = defaultdict(list)
         for addr, src, dst in algo_step.sends:
             arrivals[(dst,) + gpus[dst].locate(addr)].append((src, addr))
         substeps = []
         for (dst, dbuf, doff), senders in arrivals.items():
             for k, (src, addr) in enumerate(senders):
-                kind = 'r' if k == 0 and (dbuf, doff) not in holds_data[dst] else 'rrc'
+                incoming = sent_content[(addr, src)]
+                present = content[dst].get(addr, frozenset())
+                fresh = k == 0 and (dbuf, doff) not in holds_data[dst]
+                if fresh or not combining or present <= incoming:
+                    kind, merged = 'r', incoming
+                elif not (present & incoming):
+                    kind, merged = 'rrc', present | incoming
+                else:
+                    raise RuntimeError(f'step {xml_step + 1}: address {addr} arriving at rank {dst} from rank {src} '
+                                       'partly overlaps what the rank already reduced (would double count)')
+                content[dst][addr] = merged
                 while len(substeps) <= k:
                     substeps.append([])
                 substeps[k].append((addr, src, dst, kind))
