@@ -1,0 +1,226 @@
+// Python bindings of the native runtime (module msccl.runtime._msccl_native).
+//
+// The surface is pointer based on purpose: device addresses and streams cross the boundary as
+// integers, so the module does not depend on PyTorch's C++ ABI and any tensor library that can
+// hand out a device pointer can drive it.
+#include <cuda_runtime.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "msccl_device.h"
+#include "symm_mem.h"
+
+namespace py = pybind11;
+
+namespace msccl {
+cudaError_t launch_exec(const ExecArgs& args, int dtype, int proto, int grid, cudaStream_t stream, bool cooperative);
+int max_coresident_ctas(int dtype, int proto);
+cudaError_t launch_twoshot_allreduce(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int dtype,
+                                     int rank, int nranks, SyncPage* const* syncs, unsigned long long timeout_ns, int ctas,
+                                     cudaStream_t stream);
+cudaError_t launch_oneshot_allreduce(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes,
+                                     int dtype, int rank, int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas,
+                                     cudaStream_t stream);
+}  // namespace msccl
+
+namespace {
+
+using msccl::SyncPage;
+
+void check_rt(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw std::runtime_error(std::string(what) + " failed: " + cudaGetErrorString(e));
+}
+
+cudaStream_t as_stream(uintptr_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+uintptr_t device_malloc(size_t bytes, bool zero) {
+  void* p = nullptr;
+  check_rt(cudaMalloc(&p, bytes), "cudaMalloc");
+  if (zero) check_rt(cudaMemset(p, 0, bytes), "cudaMemset");
+  return reinterpret_cast<uintptr_t>(p);
+}
+
+void device_free(uintptr_t p) { cudaFree(reinterpret_cast<void*>(p)); }
+
+void device_memset(uintptr_t p, int value, size_t bytes) {
+  check_rt(cudaMemset(reinterpret_cast<void*>(p), value, bytes), "cudaMemset");
+  check_rt(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+}
+
+uintptr_t upload(const py::bytes& data) {
+  std::string s = data;
+  void* p = nullptr;
+  check_rt(cudaMalloc(&p, s.size() ? s.size() : 16), "cudaMalloc");
+  check_rt(cudaMemcpy(p, s.data(), s.size(), cudaMemcpyHostToDevice), "cudaMemcpy");
+  return reinterpret_cast<uintptr_t>(p);
+}
+
+void upload_into(uintptr_t dst, const py::bytes& data, uintptr_t stream) {
+  std::string s = data;
+  check_rt(cudaMemcpyAsync(reinterpret_cast<void*>(dst), s.data(), s.size(), cudaMemcpyHostToDevice, as_stream(stream)),
+           "cudaMemcpyAsync");
+  check_rt(cudaStreamSynchronize(as_stream(stream)), "cudaStreamSynchronize");
+}
+
+py::bytes download(uintptr_t src, size_t bytes) {
+  std::string s(bytes, '\0');
+  check_rt(cudaMemcpy(s.data(), reinterpret_cast<void*>(src), bytes, cudaMemcpyDeviceToHost), "cudaMemcpy");
+  return py::bytes(s);
+}
+
+// status words of a sync page: [code, rank, tb, step, iteration, aux0, aux1]
+std::vector<unsigned int> read_status(uintptr_t sync_page) {
+  std::vector<unsigned int> out(7);
+  auto* page = reinterpret_cast<SyncPage*>(sync_page);
+  check_rt(cudaMemcpy(out.data(), page->status, sizeof(unsigned int) * 7, cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
+  return out;
+}
+
+void clear_status(uintptr_t sync_page) {
+  auto* page = reinterpret_cast<SyncPage*>(sync_page);
+  check_rt(cudaMemset(&page->abort_flag, 0, sizeof(unsigned int) * 8), "cudaMemset(status)");
+}
+
+void launch(uintptr_t tbs, uintptr_t steps, uintptr_t ranks, long long chunk_elems, long long tile_elems,
+            long long slot_bytes, int iterations, int nranks, unsigned long long timeout_ns,
+            int first_tb, int grid, int dtype, int proto, uintptr_t stream, bool cooperative, bool bufs_from_args,
+            uintptr_t buf_in, uintptr_t buf_out, uintptr_t buf_scratch) {
+  msccl::ExecArgs a;
+  a.tbs = reinterpret_cast<const msccl::DevTb*>(tbs);
+  a.steps = reinterpret_cast<const msccl::DevStep*>(steps);
+  a.ranks = reinterpret_cast<const msccl::RankCtx*>(ranks);
+  a.chunk_elems = chunk_elems;
+  a.tile_elems = tile_elems;
+  a.slot_bytes = slot_bytes;
+  a.iterations = iterations;
+  a.nranks = nranks;
+  a.timeout_ns = timeout_ns;
+  a.first_tb = first_tb;
+  a.bufs_from_args = bufs_from_args ? 1 : 0;
+  a.local_buf[0] = reinterpret_cast<void*>(buf_in);
+  a.local_buf[1] = reinterpret_cast<void*>(buf_out);
+  a.local_buf[2] = reinterpret_cast<void*>(buf_scratch);
+  check_rt(msccl::launch_exec(a, dtype, proto, grid, as_stream(stream), cooperative), "launch of the MSCCL-IR executor kernel");
+}
+
+py::dict layout() {
+  py::dict d;
+  d["sizeof_SyncPage"] = sizeof(SyncPage);
+  d["sizeof_DevStep"] = sizeof(msccl::DevStep);
+  d["sizeof_DevTb"] = sizeof(msccl::DevTb);
+  d["sizeof_RankCtx"] = sizeof(msccl::RankCtx);
+  d["kMaxRanks"] = msccl::kMaxRanks;
+  d["kMaxChannels"] = msccl::kMaxChannels;
+  d["kMaxTbsPerRank"] = msccl::kMaxTbsPerRank;
+  d["kFifoSlots"] = msccl::kFifoSlots;
+  d["kExecThreads"] = msccl::kExecThreads;
+  return d;
+}
+
+py::dict vmm_create(int device, size_t size, size_t granularity) {
+  msccl::VmmBlock b = msccl::vmm_create(device, size, granularity);
+  py::dict d;
+  d["ptr"] = reinterpret_cast<uintptr_t>(b.ptr);
+  d["size"] = b.size;
+  d["handle"] = b.handle;
+  d["fd"] = b.fd;
+  return d;
+}
+
+py::dict vmm_import(int device, int fd, size_t size, size_t granularity) {
+  msccl::VmmBlock b = msccl::vmm_import(device, fd, size, granularity);
+  py::dict d;
+  d["ptr"] = reinterpret_cast<uintptr_t>(b.ptr);
+  d["size"] = b.size;
+  d["handle"] = b.handle;
+  d["fd"] = b.fd;
+  return d;
+}
+
+void vmm_release(uintptr_t ptr, size_t size, unsigned long long handle, int fd) {
+  msccl::VmmBlock b;
+  b.ptr = reinterpret_cast<void*>(ptr);
+  b.size = size;
+  b.handle = handle;
+  b.fd = fd;
+  msccl::vmm_release(b);
+}
+
+std::vector<SyncPage*> sync_list(const std::vector<uintptr_t>& v) {
+  std::vector<SyncPage*> out;
+  for (auto p : v) out.push_back(reinterpret_cast<SyncPage*>(p));
+  return out;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(_msccl_native, m) {
+  m.doc() = "Native runtime of the msccl B200 executor";
+  m.def("layout", &layout);
+  m.def("device_malloc", &device_malloc, py::arg("bytes"), py::arg("zero") = true);
+  m.def("device_free", &device_free);
+  m.def("device_memset", &device_memset);
+  m.def("upload", &upload);
+  m.def("upload_into", &upload_into);
+  m.def("download", &download);
+  m.def("read_status", &read_status);
+  m.def("clear_status", &clear_status);
+  m.def("launch", &launch, py::call_guard<py::gil_scoped_release>());
+  m.def("max_coresident_ctas", &msccl::max_coresident_ctas);
+
+  m.def("vmm_granularity", &msccl::vmm_granularity);
+  m.def("multicast_supported", &msccl::multicast_supported);
+  m.def("vmm_create", &vmm_create);
+  m.def("vmm_import", &vmm_import);
+  m.def("vmm_release", &vmm_release);
+  m.def("multicast_create", [](int n, size_t size) {
+    int fd = -1;
+    unsigned long long h = msccl::multicast_create(n, size, &fd);
+    return py::make_tuple(h, fd);
+  });
+  m.def("multicast_import", &msccl::multicast_import);
+  m.def("multicast_add_device", &msccl::multicast_add_device);
+  m.def("multicast_bind", &msccl::multicast_bind);
+  m.def("multicast_map", [](unsigned long long mc, size_t size, size_t gran, int dev) {
+    return reinterpret_cast<uintptr_t>(msccl::multicast_map(mc, size, gran, dev));
+  });
+  m.def("multicast_unmap", [](uintptr_t p, size_t size, unsigned long long mc, int dev) {
+    msccl::multicast_unmap(reinterpret_cast<void*>(p), size, mc, dev);
+  });
+  m.def("ipc_export", [](uintptr_t p) { return py::bytes(msccl::ipc_export(reinterpret_cast<void*>(p))); });
+  m.def("ipc_import", [](const py::bytes& b) { return reinterpret_cast<uintptr_t>(msccl::ipc_import(std::string(b))); });
+  m.def("ipc_close", [](uintptr_t p) { msccl::ipc_close(reinterpret_cast<void*>(p)); });
+  m.def("fd_socket_open", &msccl::fd_socket_open);
+  m.def("fd_socket_send", &msccl::fd_socket_send);
+  m.def("fd_socket_recv", [](int sock) {
+    int tag = -1;
+    int fd = msccl::fd_socket_recv(sock, &tag);
+    return py::make_tuple(fd, tag);
+  }, py::call_guard<py::gil_scoped_release>());
+  m.def("fd_socket_close", &msccl::fd_socket_close);
+
+  // In-place all-reduce of `bytes` at `offset` of every rank's symmetric heap.  mc_base = 0
+  // selects peer loads/stores, otherwise the NVLink multicast window is used.
+  m.def("twoshot_allreduce", [](uintptr_t heap_bases_dev, uintptr_t mc_base, long long offset, long long bytes, int dtype,
+                                 int rank, int nranks, uintptr_t syncs_dev, unsigned long long timeout_ns, int ctas,
+                                 uintptr_t stream) {
+    check_rt(msccl::launch_twoshot_allreduce(reinterpret_cast<char* const*>(heap_bases_dev), reinterpret_cast<char*>(mc_base),
+                                             offset, bytes, dtype, rank, nranks,
+                                             reinterpret_cast<SyncPage* const*>(syncs_dev), timeout_ns, ctas, as_stream(stream)),
+             "launch of the two-shot all-reduce kernel");
+  });
+  // Out-of-place all-reduce of a small message through LL staging slots on every rank.
+  m.def("oneshot_allreduce", [](uintptr_t in, uintptr_t out, uintptr_t staging_dev, long long bytes, long long slot_bytes,
+                                 int dtype, int rank, int nranks, uintptr_t sync, unsigned long long timeout_ns, int ctas,
+                                 uintptr_t stream) {
+    check_rt(msccl::launch_oneshot_allreduce(reinterpret_cast<const void*>(in), reinterpret_cast<void*>(out),
+                                             reinterpret_cast<char* const*>(staging_dev), bytes, slot_bytes, dtype, rank,
+                                             nranks, reinterpret_cast<SyncPage*>(sync), timeout_ns, ctas, as_stream(stream)),
+             "launch of the one-shot all-reduce kernel");
+  });
+}

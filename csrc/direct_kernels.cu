@@ -1,0 +1,255 @@
+// Direct (non-interpreted) all-reduce kernels over symmetric memory for one NVSwitch box.
+//
+//   one-shot LL  : every rank pushes its whole message into a private staging slot on every
+//                  peer as 16-byte {data, flag, data, flag} packets and then sums the n slots in
+//                  rank order.  One NVLink traversal, no barrier, no fence: the latency floor
+//                  for small messages.  Input and output may be ordinary device memory.
+//   two-shot     : in place on a symmetric buffer.  Rank r owns 1/n of the message: it reduces
+//                  that slice across all ranks and publishes the result to all ranks.
+//                  NVLS mode does both inside the switch (multimem.ld_reduce + multimem.st on the
+//                  multicast window); P2P mode uses plain peer loads and stores, summing in rank
+//                  order so that all ranks produce identical bits.
+//
+// All waits are bounded; on expiry the kernel writes a status code to the rank's sync page and
+// returns.  These are the hand-tuned counterparts of the allreduce_one_shot / allreduce_two_shot
+// MSCCLang programs (msccl/programs/allreduce.py), selected by the plan dispatcher by size.
+#include "msccl_device.h"
+#include "prims.cuh"
+
+namespace msccl {
+
+namespace {
+
+constexpr int kDirectThreads = 512;
+
+__device__ __forceinline__ void fail_direct(SyncPage* sync, unsigned int code, int rank, unsigned int aux0, unsigned int aux1) {
+  if (atomicCAS(&sync->status[0], 0u, code) == 0u) {
+    sync->status[1] = rank;
+    sync->status[2] = blockIdx.x;
+    sync->status[3] = 0;
+    sync->status[4] = 0;
+    sync->status[5] = aux0;
+    sync->status[6] = aux1;
+  }
+  __threadfence();
+  atomicExch(&sync->abort_flag, 1u);
+}
+
+// Barrier across ranks for CTA lane blockIdx.x.  Returns false if it timed out.
+__device__ bool rank_barrier(SyncPage* const* syncs, int rank, int nranks, unsigned long long deadline, int* s_fail) {
+  SyncPage* me = syncs[rank];
+  const int lane = blockIdx.x;
+  __syncthreads();
+  if (threadIdx.x < nranks) {
+    const unsigned long long e = me->cta_epoch[lane] + 1;
+    __threadfence_system();
+    st_release_sys(&syncs[threadIdx.x]->cta_barrier[lane][rank], e);
+    unsigned int spins = 0;
+    while (ld_acquire_sys(&me->cta_barrier[lane][threadIdx.x]) < e) {
+      if ((++spins & 127u) == 0 && (global_timer_ns() > deadline || ld_volatile_u32(&me->abort_flag) != 0)) {
+        *reinterpret_cast<volatile int*>(s_fail) = 1;
+        fail_direct(me, STATUS_TIMEOUT_BARRIER, rank, threadIdx.x, lane);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) me->cta_epoch[lane] = me->cta_epoch[lane] + 1;
+  __syncthreads();
+  return *reinterpret_cast<volatile int*>(s_fail) == 0;
+}
+
+// ---- multimem wrappers ---------------------------------------------------------------------
+template <typename T> struct Multimem;
+
+template <> struct Multimem<float> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+                 ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1,%2,%3,%4};"
+                 ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+template <> struct Multimem<__half> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ void st(void* p, uint4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1,%2,%3,%4};"
+                 ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+};
+
+// ---- two-shot, in place on a symmetric buffer ---------------------------------------------
+// heap_bases[r] + offset = rank r's buffer as mapped here (P2P mode); mc = the same offset inside
+// the multicast window (NVLS mode).
+template <typename T, bool NVLS>
+__global__ void __launch_bounds__(kDirectThreads, 1)
+twoshot_allreduce_kernel(char* const* heap_bases, char* mc, long long offset, long long bytes, int rank, int nranks,
+                         SyncPage* const* syncs, unsigned long long timeout_ns) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const unsigned long long deadline = global_timer_ns() + timeout_ns;
+  if (!rank_barrier(syncs, rank, nranks, deadline, &s_fail)) return;   // every rank's input is in place
+
+  // slice of this rank, then of this CTA, in 16-byte vectors
+  const long long vectors = bytes / 16;
+  const long long per_rank = (vectors + nranks - 1) / nranks;
+  const long long r_begin = min(vectors, per_rank * rank), r_end = min(vectors, r_begin + per_rank);
+  const long long per_cta = (r_end - r_begin + gridDim.x - 1) / gridDim.x;
+  const long long begin = min(r_end, r_begin + per_cta * blockIdx.x), end = min(r_end, begin + per_cta);
+
+  if (NVLS) {
+    constexpr int U = 4;
+    for (long long v = begin + threadIdx.x; v < end; v += static_cast<long long>(blockDim.x) * U) {
+      uint4 acc[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        long long i = v + static_cast<long long>(u) * blockDim.x;
+        if (i < end) acc[u] = Multimem<T>::ld_reduce(mc + i * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        long long i = v + static_cast<long long>(u) * blockDim.x;
+        if (i < end) Multimem<T>::st(mc + i * 16, acc[u]);
+      }
+    }
+  } else {
+    for (long long v = begin + threadIdx.x; v < end; v += blockDim.x) {
+      uint4 acc = *reinterpret_cast<const uint4*>(heap_bases[0] + offset + v * 16);
+      for (int r = 1; r < nranks; ++r)
+        acc = Vec16<T>::add(acc, *reinterpret_cast<const uint4*>(heap_bases[r] + offset + v * 16));
+      for (int r = 0; r < nranks; ++r) *reinterpret_cast<uint4*>(heap_bases[(rank + r) % nranks] + offset + v * 16) = acc;
+    }
+  }
+  rank_barrier(syncs, rank, nranks, deadline, &s_fail);               // every slice has been published
+}
+
+// ---- one-shot LL ---------------------------------------------------------------------------
+// staging[r] = rank r's staging area as mapped here: [2 parities][nranks senders][slot_bytes],
+// slot_bytes >= 2 * message bytes (a packet carries 8 bytes of payload per 16).
+template <typename T>
+__global__ void __launch_bounds__(kDirectThreads, 1)
+oneshot_ll_allreduce_kernel(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes,
+                            int rank, int nranks, SyncPage* sync, unsigned long long timeout_ns) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const unsigned long long deadline = global_timer_ns() + timeout_ns;
+  const unsigned long long epoch = sync->ll_epoch + 1;       // same value on every rank (all launch in lockstep)
+  const unsigned int flag = static_cast<unsigned int>(epoch);
+  const long long parity_off = static_cast<long long>(epoch & 1) * nranks * slot_bytes;
+  const long long vectors = bytes / 16;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+
+  // push: my vector v goes to slot [parity][rank] of every rank (including myself)
+  for (long long v = tid; v < vectors; v += nthreads) {
+    const uint4 d = *reinterpret_cast<const uint4*>(static_cast<const char*>(in) + v * 16);
+    const uint4 p0 = make_uint4(d.x, flag, d.y, flag), p1 = make_uint4(d.z, flag, d.w, flag);
+    for (int r = 0; r < nranks; ++r) {
+      uint4* pk = reinterpret_cast<uint4*>(staging[(rank + r) % nranks] + parity_off + rank * slot_bytes) + 2 * v;
+      st_volatile_v4(pk, p0);
+      st_volatile_v4(pk + 1, p1);
+    }
+  }
+  // pull: sum the n slots of my own staging area in rank order
+  const char* mine = staging[rank] + parity_off;
+  for (long long v = tid; v < vectors; v += nthreads) {
+    uint4 acc;
+    for (int r = 0; r < nranks; ++r) {
+      const uint4* pk = reinterpret_cast<const uint4*>(mine + r * slot_bytes) + 2 * v;
+      uint4 a, b;
+      unsigned int spins = 0;
+      while (true) {
+        a = ld_volatile_v4(pk);
+        b = ld_volatile_v4(pk + 1);
+        if (a.y == flag && a.w == flag && b.y == flag && b.w == flag) break;
+        if ((++spins & 255u) == 0 && (s_fail != 0 || global_timer_ns() > deadline)) {
+          if (atomicExch(&s_fail, 1) == 0) fail_direct(sync, STATUS_TIMEOUT_DATA, rank, r, 0);
+          break;
+        }
+      }
+      const uint4 d = make_uint4(a.x, a.z, b.x, b.z);
+      acc = (r == 0) ? d : Vec16<T>::add(acc, d);
+    }
+    *reinterpret_cast<uint4*>(static_cast<char*>(out) + v * 16) = acc;
+  }
+  // the last CTA to finish advances the epoch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&sync->ll_done, 1u) == gridDim.x - 1u) {
+      sync->ll_done = 0;
+      sync->ll_epoch = epoch;
+    }
+  }
+}
+
+template <typename T>
+cudaError_t twoshot_typed(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int rank, int nranks,
+                          SyncPage* const* syncs, unsigned long long timeout_ns, int ctas, cudaStream_t stream) {
+  if (mc_base != nullptr) {
+    twoshot_allreduce_kernel<T, true><<<ctas, kDirectThreads, 0, stream>>>(heap_bases, mc_base + offset, offset, bytes, rank,
+                                                                         nranks, syncs, timeout_ns);
+  } else {
+    twoshot_allreduce_kernel<T, false><<<ctas, kDirectThreads, 0, stream>>>(heap_bases, nullptr, offset, bytes, rank, nranks,
+                                                                          syncs, timeout_ns);
+  }
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t oneshot_typed(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes, int rank,
+                          int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas, cudaStream_t stream) {
+  oneshot_ll_allreduce_kernel<T><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync,
+                                                                     timeout_ns);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_twoshot_allreduce(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int dtype,
+                                     int rank, int nranks, SyncPage* const* syncs, unsigned long long timeout_ns, int ctas,
+                                     cudaStream_t stream) {
+  if (bytes % 16 != 0 || offset % 16 != 0 || ctas < 1 || ctas > kMaxDirectCtas || nranks > kMaxRanks) return cudaErrorInvalidValue;
+  switch (dtype) {
+    case DT_F32: return twoshot_typed<float>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream);
+    case DT_BF16: return twoshot_typed<__nv_bfloat16>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream);
+    case DT_F16: return twoshot_typed<__half>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t launch_oneshot_allreduce(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes,
+                                     int dtype, int rank, int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas,
+                                     cudaStream_t stream) {
+  if (bytes % 16 != 0 || 2 * bytes > slot_bytes || ctas < 1 || nranks > kMaxRanks) return cudaErrorInvalidValue;
+  switch (dtype) {
+    case DT_F32: return oneshot_typed<float>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns, ctas, stream);
+    case DT_BF16: return oneshot_typed<__nv_bfloat16>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns, ctas, stream);
+    case DT_F16: return oneshot_typed<__half>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns, ctas, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace msccl

@@ -1,0 +1,222 @@
+"""Executor: runs MSCCL-IR programs and the direct all-reduce kernels on a ``Communicator``.
+
+``Executor.run(plan, ...)`` launches the interpreter kernel for one compiled program.
+``Executor.all_reduce / all_gather / reduce_scatter / all_to_all`` pick a program from the plan
+table by message size (the ``<msccl_algos>`` table ``msccl.init`` writes, reference
+``msccl/autosynth/__init__.py:75-94``), or for all-reduce one of the direct kernels:
+
+* message <= ``comm.ll_max_bytes``         -> one-shot LL kernel (any device memory);
+* tensor inside the symmetric arena          -> two-shot in place (NVLS multimem when the heap is
+                                               bound to a multicast object, peer loads otherwise);
+* otherwise                                  -> the interpreter with the registered program.
+"""
+import math
+import os
+
+import torch
+
+from msccl.runtime.comm import Communicator
+from msccl.runtime.plan import (HostPlan, PlanError, chunk_geometry, compile_plan, tile_geometry, K_FIFO_SLOTS)
+from msccl.xml.loader import AlgoIR, load_plan_table, load_xml
+
+DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+MAX_SLOT_BYTES = 4 << 20
+
+
+class DevicePlan:
+    """A ``HostPlan`` uploaded to the device, bound to one communicator."""
+
+    def __init__(self, comm: Communicator, algo: AlgoIR):
+        self.comm = comm
+        self.algo = algo
+        if algo.ngpus != comm.world:
+            raise PlanError(f'program is for {algo.ngpus} GPUs, communicator has {comm.world}')
+        from msccl.runtime.plan import fifo_index_tables
+        conns = max((len(t) for t in fifo_index_tables(algo).values()), default=0)
+        slot = MAX_SLOT_BYTES if conns == 0 else min(MAX_SLOT_BYTES, comm.fifo_bytes // (conns * K_FIFO_SLOTS))
+        self.slot_bytes = slot // 1024 * 1024
+        if self.slot_bytes < 1024:
+            raise PlanError('FIFO area too small for this program')
+        self.host: HostPlan = compile_plan(algo, comm.local_ranks, self.slot_bytes)
+        nat = comm.native
+        self.dev_tbs = nat.upload(self.host.tb_bytes)
+        self.dev_steps = nat.upload(self.host.step_bytes)
+        self.grid = self.host.total_tbs()
+        self.scratch = {}
+
+    def close(self):
+        for p in (self.dev_tbs, self.dev_steps):
+            self.comm.native.device_free(p)
+        self.scratch = {}
+
+
+class Executor:
+    def __init__(self, comm: Communicator):
+        self.comm = comm
+        self.table = {}            # collective -> [(min_bytes, max_bytes, DevicePlan)]
+        self.launches = 0          # kernels launched by this executor (for reporting)
+        self._checked_grid = {}
+
+    # ------------------------------------------------------------------ plans
+    def compile(self, algo_or_xml) -> DevicePlan:
+        algo = load_xml(algo_or_xml) if isinstance(algo_or_xml, str) else algo_or_xml
+        return DevicePlan(self.comm, algo)
+
+    def register(self, algo_or_xml, min_bytes=0, max_bytes=math.inf):
+        plan = self.compile(algo_or_xml)
+        self.table.setdefault(plan.algo.coll, []).append((min_bytes, max_bytes, plan))
+        return plan
+
+    def load_plan_table(self, path=None):
+        """Install the plans of an ``<msccl_algos>`` file (default: ``$MSCCL_CONFIG``)."""
+        path = path or os.environ.get('MSCCL_CONFIG')
+        if not path:
+            raise PlanError('no plan table: call msccl.init(...) first or pass a path')
+        for entry in load_plan_table(path):
+            if entry.algo.ngpus == self.comm.world:
+                self.register(entry.algo, entry.min_bytes, entry.max_bytes)
+        return self
+
+    def select(self, collective, nbytes):
+        for lo, hi, plan in self.table.get(collective, []):
+            if lo <= nbytes < hi:
+                return plan
+        return None
+
+    # ------------------------------------------------------------- interpreter
+    def run(self, plan: DevicePlan, inputs, outputs=None, stream=None):
+        """Execute ``plan``.  ``inputs`` / ``outputs`` map every local rank to a contiguous CUDA
+        tensor (a bare tensor is accepted when this process runs one rank).  For in-place
+        programs ``outputs`` may be omitted.  Returns the output tensors by rank."""
+        comm, algo = self.comm, plan.algo
+        if torch.is_tensor(inputs):
+            inputs = {comm.local_ranks[0]: inputs}
+        if torch.is_tensor(outputs):
+            outputs = {comm.local_ranks[0]: outputs}
+        outputs = outputs or {}
+        first = inputs[comm.local_ranks[0]]
+        dtype = first.dtype
+        if dtype not in DTYPE_CODES:
+            raise PlanError(f'unsupported dtype {dtype}')
+        esize = first.element_size()
+        chunk = chunk_geometry(algo, comm.local_ranks[0], first.numel())
+        tile, iterations = tile_geometry(plan.host, chunk, esize, plan.slot_bytes)
+        buffers, results = {}, {}
+        for r in comm.local_ranks:
+            g = algo.gpus[r]
+            t_in = inputs[r]
+            assert t_in.is_cuda and t_in.is_contiguous() and t_in.dtype == dtype
+            used = plan.host.extents[r]
+            in_ptr, out_ptr = t_in.data_ptr(), 0
+            if algo.inplace and algo.coll == 'allgather':
+                # the caller's tensor is the gathered buffer; its own part is already in place
+                out_t = outputs.get(r, t_in)
+                if out_t.numel() != g.o_chunks * chunk:
+                    raise PlanError(f'in-place all-gather needs the full {g.o_chunks * chunk}-element buffer')
+                in_ptr, out_ptr, results[r] = 0, out_t.data_ptr(), out_t
+            else:
+                if t_in.numel() < used['i'] * chunk:
+                    raise PlanError(f'rank {r}: input of {t_in.numel()} elements, program reads {used["i"] * chunk}')
+                if used['o'] > 0:
+                    out_t = outputs.get(r)
+                    if out_t is None:
+                        out_t = torch.empty(g.o_chunks * chunk, dtype=dtype, device=t_in.device)
+                    if out_t.numel() < used['o'] * chunk:
+                        raise PlanError(f'rank {r}: output of {out_t.numel()} elements, program writes {used["o"] * chunk}')
+                    out_ptr, results[r] = out_t.data_ptr(), out_t
+                else:
+                    results[r] = t_in
+            scratch_ptr = 0
+            if used['s'] > 0:
+                need = used['s'] * chunk * esize
+                have = plan.scratch.get(r)
+                if have is None or have.numel() < need:
+                    have = torch.empty(need, dtype=torch.uint8, device=t_in.device)
+                    plan.scratch[r] = have
+                scratch_ptr = have.data_ptr()
+            for p in (in_ptr, out_ptr, scratch_ptr):
+                if p % 16 != 0:
+                    raise PlanError('buffers must be 16-byte aligned')
+            buffers[r] = (in_ptr, out_ptr, scratch_ptr)
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        nat = comm.native
+        key = (DTYPE_CODES[dtype], plan.host.proto)
+        if key not in self._checked_grid:
+            self._checked_grid[key] = nat.max_coresident_ctas(*key)
+        if plan.grid > self._checked_grid[key]:
+            raise PlanError(f'{plan.grid} threadblocks cannot be co-resident on this device '
+                            f'(limit {self._checked_grid[key]})')
+        if comm.emulated_mode:
+            nat.upload_into(comm.dev_rankctx, comm.rankctx_bytes(buffers), stream_h)
+            b = (0, 0, 0)
+        else:
+            b = buffers[comm.rank]
+        nat.launch(plan.dev_tbs, plan.dev_steps, comm.dev_rankctx, chunk, tile, plan.slot_bytes, iterations,
+                   comm.world, comm.timeout_ns, 0, plan.grid, key[0], key[1], stream_h, True,
+                   not comm.emulated_mode, b[0], b[1], b[2])
+        self.launches += 1
+        return results
+
+    # -------------------------------------------------------------- collectives
+    def all_reduce(self, tensor, stream=None, algorithm='auto'):
+        """In-place sum over all ranks.  ``algorithm``: auto | oneshot | twoshot | xml."""
+        comm = self.comm
+        if comm.emulated_mode:
+            raise PlanError('collective entry points need one process per GPU; use run() with an emulated communicator')
+        nbytes = tensor.numel() * tensor.element_size()
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        code = DTYPE_CODES[tensor.dtype]
+        if comm.world == 1:
+            return tensor
+        offset = comm.heap_offset_of(tensor)
+        if algorithm == 'auto':
+            if nbytes <= comm.ll_max_bytes and nbytes % 16 == 0:
+                algorithm = 'oneshot'
+            elif offset is not None and nbytes % 16 == 0:
+                algorithm = 'twoshot'
+            else:
+                algorithm = 'xml'
+        if algorithm == 'oneshot':
+            ctas = max(1, min(16, nbytes // (16 * 512 * 2) or 1))
+            comm.native.oneshot_allreduce(tensor.data_ptr(), tensor.data_ptr(), comm.dev_staging, nbytes,
+                                          comm.ll_slot_bytes, code, comm.rank, comm.world, comm.sync_ptr(comm.rank),
+                                          comm.timeout_ns, ctas, stream_h)
+            self.launches += 1
+            return tensor
+        if algorithm == 'twoshot':
+            if offset is None:
+                raise PlanError('two-shot all-reduce needs a tensor from Communicator.symmetric_empty')
+            ctas = int(os.environ.get('MSCCL_TWOSHOT_CTAS', '0')) or max(1, min(32, nbytes // (256 << 10) or 1))
+            comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, offset, nbytes, code, comm.rank,
+                                          comm.world, comm.dev_syncs, comm.timeout_ns, ctas, stream_h)
+            self.launches += 1
+            return tensor
+        plan = self.select('allreduce', nbytes)
+        if plan is None:
+            raise PlanError(f'no all-reduce plan registered for {nbytes} bytes')
+        flat = tensor.view(-1)
+        if plan.algo.inplace:
+            self.run(plan, flat, stream=stream)
+        else:
+            out = self.run(plan, flat, stream=stream)[comm.rank]
+            flat.copy_(out[:flat.numel()])
+        return tensor
+
+    def _run_registered(self, collective, inp, out, stream):
+        nbytes = inp.numel() * inp.element_size()
+        plan = self.select(collective, nbytes)
+        if plan is None:
+            raise PlanError(f'no {collective} plan registered for {nbytes} bytes')
+        return self.run(plan, inp.view(-1), out.view(-1) if out is not None else None, stream=stream)[self.comm.rank]
+
+    def all_gather(self, output, input, stream=None):
+        return self._run_registered('allgather', input, output, stream)
+
+    def reduce_scatter(self, output, input, stream=None):
+        return self._run_registered('reduce_scatter', input, output, stream)
+
+    def all_to_all(self, output, input, stream=None):
+        return self._run_registered('alltoall', input, output, stream)
+
+    def check(self):
+        self.comm.check()
