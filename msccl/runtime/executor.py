@@ -99,7 +99,11 @@ class Executor:
         if dtype not in DTYPE_CODES:
             raise PlanError(f'unsupported dtype {dtype}')
         esize = first.element_size()
-        chunk = chunk_geometry(algo, comm.local_ranks[0], first.numel())
+        if algo.inplace and algo.coll == 'allgather':
+            # the caller passes the gathered buffer with its own part already in place
+            chunk = first.numel() // max(algo.gpus[comm.local_ranks[0]].o_chunks, 1)
+        else:
+            chunk = chunk_geometry(algo, comm.local_ranks[0], first.numel())
         tile, iterations = tile_geometry(plan.host, chunk, esize, plan.slot_bytes)
         buffers, results = {}, {}
         for r in comm.local_ranks:

