@@ -12,6 +12,7 @@
 #include <string>
 #include <vector>
 
+#include "gemm_sm100.h"
 #include "msccl_device.h"
 #include "symm_mem.h"
 
@@ -199,11 +200,23 @@ PYBIND11_MODULE(_msccl_native, m) {
   m.def("fd_socket_send", &msccl::fd_socket_send);
   m.def("fd_socket_recv", [](int sock) {
     int tag = -1;
-    int fd = msccl::fd_socket_recv(sock, &tag);
+    int fd = -1;
+    {
+      py::gil_scoped_release release;      // blocking receive; Python objects are built after re-acquiring
+      fd = msccl::fd_socket_recv(sock, &tag);
+    }
     return py::make_tuple(fd, tag);
-  }, py::call_guard<py::gil_scoped_release>());
+  });
   m.def("fd_socket_close", &msccl::fd_socket_close);
 
+  // D = epilogue(A[M,K] * B[N,K]^T) with the tcgen05 kernel; error_words: 4 ints of device memory (or 0).
+  m.def("gemm_bf16", [](uintptr_t a, uintptr_t b, uintptr_t d, int M, int N, int K, int lda, int ldb, int ldd, int epilogue,
+                         int bn, uintptr_t error_words, int max_ctas, uintptr_t stream) {
+    check_rt(msccl::sm100::gemm_bf16(reinterpret_cast<const void*>(a), reinterpret_cast<const void*>(b),
+                                     reinterpret_cast<void*>(d), M, N, K, lda, ldb, ldd, epilogue, bn,
+                                     reinterpret_cast<int*>(error_words), max_ctas, as_stream(stream)),
+             "launch of the tcgen05 GEMM kernel");
+  });
   // In-place all-reduce of `bytes` at `offset` of every rank's symmetric heap.  mc_base = 0
   // selects peer loads/stores, otherwise the NVLink multicast window is used.
   m.def("twoshot_allreduce", [](uintptr_t heap_bases_dev, uintptr_t mc_base, long long offset, long long bytes, int dtype,
