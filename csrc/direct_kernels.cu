@@ -119,7 +119,7 @@ twoshot_allreduce_kernel(char* const* heap_bases, char* mc, long long offset, lo
   const long long begin = min(r_end, r_begin + per_cta * blockIdx.x), end = min(r_end, begin + per_cta);
 
   if (NVLS) {
-    constexpr int U = 4;
+    constexpr int U = 8;
     for (long long v = begin + threadIdx.x; v < end; v += static_cast<long long>(blockDim.x) * U) {
       uint4 acc[U];
 #pragma unroll

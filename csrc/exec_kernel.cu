@@ -284,10 +284,16 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
   // everything (the next launch may use another layout).
   if (tid == 0) {
     if (!failed && has_send && !w.until_ge(&sync->send_head[send_conn], sseq, true)) {
-      record_failure(sync, STATUS_TIMEOUT_DRAIN, tb.rank, tb.tb_in_rank, tb.nsteps, a.iterations, tb.send_peer, tb.chan);
+      record_failure(sync, STATUS_TIMEOUT_DRAIN, my_rank, my_tb, nsteps, a.iterations, send_peer_id, chan);
     }
-    if (has_send) sync->send_seq[tb.send_conn] = sseq;
-    if (has_recv) sync->recv_seq[tb.recv_conn] = rseq;
+    if (has_send) sync->send_seq[send_conn] = sseq;
+    if (has_recv) sync->recv_seq[recv_conn] = rseq;
+    // the last threadblock of this rank to finish advances the launch epoch
+    __threadfence();
+    if (atomicAdd(&sync->exec_done, 1u) == static_cast<unsigned int>(tb.tbs_in_rank) - 1u) {
+      sync->exec_done = 0;
+      sync->exec_epoch = epoch;
+    }
   }
 }
 

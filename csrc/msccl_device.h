@@ -26,7 +26,7 @@ constexpr int kMaxConns = kMaxRanks * kMaxChannels;   // connection id = chan * 
 constexpr int kMaxTbsPerRank = 128;
 constexpr int kFifoSlots = 4;                          // tiles in flight per connection
 constexpr int kExecThreads = 512;
-constexpr int kMaxDirectCtas = 64;                     // CTAs of the direct (non-interpreted) kernels
+constexpr int kMaxDirectCtas = 160;                     // CTAs of the direct (non-interpreted) kernels
 
 // Error codes written to SyncPage::status[0]; 0 means success.
 enum StatusCode : uint32_t {

@@ -190,7 +190,7 @@ class Executor:
         if algorithm == 'twoshot':
             if offset is None:
                 raise PlanError('two-shot all-reduce needs a tensor from Communicator.symmetric_empty')
-            ctas = int(os.environ.get('MSCCL_TWOSHOT_CTAS', '0')) or max(1, min(32, nbytes // (256 << 10) or 1))
+            ctas = int(os.environ.get('MSCCL_TWOSHOT_CTAS', '0')) or max(1, min(128, nbytes // (128 << 10) or 1))
             comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, offset, nbytes, code, comm.rank,
                                           comm.world, comm.dev_syncs, comm.timeout_ns, ctas, stream_h)
             self.launches += 1
