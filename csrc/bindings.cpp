@@ -12,6 +12,7 @@
 #include <string>
 #include <vector>
 
+#include "fused_tp.h"
 #include "gemm_sm100.h"
 #include "msccl_device.h"
 #include "symm_mem.h"
@@ -217,6 +218,49 @@ PYBIND11_MODULE(_msccl_native, m) {
                                      reinterpret_cast<int*>(error_words), max_ctas, as_stream(stream)),
              "launch of the tcgen05 GEMM kernel");
   });
+  // Fused all-gather -> GEMM (epilogue 0: plain, 1: SwiGLU).  heap_ptrs: every rank's heap base in this process.
+  m.def("ag_gemm", [](uintptr_t x_local, uintptr_t b, uintptr_t d, int rows_per_rank, int N, int K, int ldb, int ldd, int rank,
+                       int nranks, int comm_ctas, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs, size_t off_fused,
+                       uintptr_t mc_base, size_t gathered_off, size_t gathered_bytes, uintptr_t error_words, int epilogue,
+                       int grid, uintptr_t stream) {
+    msccl::sm100::AgGemmArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.x_local = reinterpret_cast<const void*>(x_local);
+    g.b = reinterpret_cast<const void*>(b);
+    g.d = reinterpret_cast<void*>(d);
+    g.rows_per_rank = rows_per_rank; g.N = N; g.K = K; g.ldb = ldb; g.ldd = ldd;
+    g.rank = rank; g.nranks = nranks; g.comm_ctas = comm_ctas;
+    g.heap_bases = reinterpret_cast<char* const*>(heap_bases_dev);
+    if (static_cast<int>(heap_ptrs.size()) != nranks || nranks > msccl::sm100::kFusedMaxRanks) throw std::runtime_error("bad rank count");
+    for (int r = 0; r < nranks; ++r) {
+      g.heap_bases_host[r] = reinterpret_cast<char*>(heap_ptrs[r]);
+      g.pages[r] = reinterpret_cast<msccl::sm100::FusedPage*>(heap_ptrs[r] + off_fused);
+    }
+    g.mc_base = reinterpret_cast<char*>(mc_base);
+    g.gathered_off = gathered_off;
+    g.gathered_bytes = gathered_bytes;
+    g.error_words = reinterpret_cast<int*>(error_words);
+    check_rt(msccl::sm100::launch_ag_gemm(g, epilogue, grid, as_stream(stream)), "launch of the fused all-gather GEMM kernel");
+  });
+  // Fused GEMM -> reduce-scatter.
+  m.def("gemm_rs", [](uintptr_t a, uintptr_t b, uintptr_t out, int rows_per_rank, int N, int K, int lda, int ldb, int rank,
+                       int nranks, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs, size_t off_fused, size_t partial_off,
+                       uintptr_t error_words, int grid, uintptr_t stream) {
+    msccl::sm100::GemmRsArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.a = reinterpret_cast<const void*>(a);
+    g.b = reinterpret_cast<const void*>(b);
+    g.out = reinterpret_cast<void*>(out);
+    g.rows_per_rank = rows_per_rank; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb;
+    g.rank = rank; g.nranks = nranks;
+    g.heap_bases = reinterpret_cast<char* const*>(heap_bases_dev);
+    if (static_cast<int>(heap_ptrs.size()) != nranks || nranks > msccl::sm100::kFusedMaxRanks) throw std::runtime_error("bad rank count");
+    for (int r = 0; r < nranks; ++r) g.pages[r] = reinterpret_cast<msccl::sm100::FusedPage*>(heap_ptrs[r] + off_fused);
+    g.partial_off = partial_off;
+    g.error_words = reinterpret_cast<int*>(error_words);
+    check_rt(msccl::sm100::launch_gemm_rs(g, grid, as_stream(stream)), "launch of the fused GEMM reduce-scatter kernel");
+  });
+  m.def("sm_count", &msccl::sm100::sm_count);
   // In-place all-reduce of `bytes` at `offset` of every rank's symmetric heap.  mc_base = 0
   // selects peer loads/stores, otherwise the NVLink multicast window is used.
   m.def("twoshot_allreduce", [](uintptr_t heap_bases_dev, uintptr_t mc_base, long long offset, long long bytes, int dtype,

@@ -1,0 +1,501 @@
+// Fused tensor-parallel kernels for sm_100a: the collective and the tcgen05 GEMM run in ONE
+// kernel and overlap tile by tile.
+//
+//   all-gather -> GEMM   D[n*Ml, N] = epilogue(gather(X)[n*Ml, K] * B[N, K]^T)
+//       A few "comm" CTAs push this rank's token shard X[Ml, K] into the gathered buffer of every
+//       rank (multimem.st through NVSwitch when a multicast window exists, else peer stores) in
+//       128-row blocks and publish one flag per block.  The other CTAs are the persistent GEMM:
+//       their TMA producer waits for the flag of the block a tile needs, then loads it from the
+//       LOCAL gathered buffer (never from peer memory, never with multicast).  Tiles are ordered
+//       block-major so that consumption follows arrival; tiles of the local shard need no flag.
+//
+//   GEMM -> reduce-scatter   Y_owner[Ml, N] = sum over ranks of (H_r[n*Ml, K] * B_r[N, K]^T)[owner rows]
+//       The epilogue converts each accumulator tile to bf16 and stores it straight into the owner
+//       rank's partial buffer over NVLink, then bumps a per-(source, row block) counter on the
+//       owner.  Tiles are ordered owner-major starting at rank+1, so at any moment every rank sends
+//       to a different peer.  When its tiles are done every CTA turns into a reducer: it waits for
+//       the counters of a row block and sums the n partials in fp32, in rank order.
+//
+// Buffers that peers write are double buffered by launch parity, so no barrier is needed between
+// consecutive calls (a rank can be at most one call ahead of a peer: it needs the peer's data of
+// call k+1 before it can finish it).  Every wait is bounded.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "gemm_sm100.cuh"
+#include "gemm_sm100.h"
+#include "fused_tp.h"
+#include "prims.cuh"
+
+namespace msccl {
+namespace sm100 {
+
+namespace {
+
+constexpr int BN = 256;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;
+constexpr int kBBytes = BN * BK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 2 * BN;
+constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256;
+constexpr unsigned int kFlagSpin = 1u << 26;
+
+__device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag, unsigned long long want, volatile int* abort_flag) {
+  for (unsigned int i = 0; i < kFlagSpin; ++i) {
+    if (ld_acquire_sys(flag) >= want) return true;
+    if ((i & 1023u) == 1023u && *abort_flag != 0) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void multimem_st16(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void red_add_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+struct Pipe {
+  uint8_t* stage_base;
+  uint64_t *full_bar, *empty_bar, *acc_full, *acc_empty;
+  uint32_t* tmem_slot;
+  volatile int* abort_flag;
+};
+
+__device__ __forceinline__ Pipe carve_smem(uint8_t* smem_raw) {
+  Pipe p;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  p.stage_base = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(kStages) * kStageBytes);
+  p.full_bar = bars;
+  p.empty_bar = bars + kStages;
+  p.acc_full = bars + 2 * kStages;
+  p.acc_empty = bars + 2 * kStages + 2;
+  p.tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  p.abort_flag = reinterpret_cast<volatile int*>(p.tmem_slot + 1);
+  return p;
+}
+
+__device__ __forceinline__ void init_pipe(const Pipe& p) {
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&p.full_bar[s], 1);
+      mbar_init(&p.empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&p.acc_full[a], 1);
+      mbar_init(&p.acc_empty[a], 4);
+    }
+    *p.abort_flag = 0;
+    mbar_fence_init();
+  }
+}
+
+// MMA issuer shared by both kernels: consumes `my_tiles` tiles of k_blocks stages each.
+__device__ __forceinline__ void mma_role(const Pipe& p, uint32_t tmem_base, int my_tiles, int k_blocks, int* error_words) {
+  constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
+  int stage = 0, acc = 0;
+  uint32_t phase = 0, acc_phase = 0;
+  for (int t = 0; t < my_tiles; ++t) {
+    if (!mbar_wait(&p.acc_empty[acc], acc_phase ^ 1, p.abort_flag)) {
+      gemm_fail(error_words, p.abort_flag, GEMM_TIMEOUT_ACC, 1, acc);
+      return;
+    }
+    tc_fence_after_sync();
+    const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+    for (int kb = 0; kb < k_blocks; ++kb) {
+      if (!mbar_wait(&p.full_bar[stage], phase, p.abort_flag)) {
+        gemm_fail(error_words, p.abort_flag, GEMM_TIMEOUT_FULL, 1, stage);
+        return;
+      }
+      tc_fence_after_sync();
+      const uint32_t a_addr = smem_u32(p.stage_base + static_cast<size_t>(stage) * kStageBytes);
+      const uint64_t adesc = smem_desc_sw128(a_addr);
+      const uint64_t bdesc = smem_desc_sw128(a_addr + kABytes);
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k)
+        umma_bf16(tmem_d, adesc + static_cast<uint64_t>(k * 2), bdesc + static_cast<uint64_t>(k * 2), idesc, (kb | k) != 0);
+      tc_commit(&p.empty_bar[stage]);
+      if (++stage == kStages) { stage = 0; phase ^= 1; }
+    }
+    tc_commit(&p.acc_full[acc]);
+    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+  }
+}
+
+__device__ __forceinline__ void drain_loads(const Pipe& p) {
+  for (int s = 0; s < kStages; ++s)
+    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&p.full_bar[s], 0) && !mbar_try_wait(&p.full_bar[s], 1); ++i) {}
+}
+
+// ============================================================ all-gather -> GEMM (+SwiGLU)
+template <int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_constant__ CUtensorMap map_gath0,
+               const __grid_constant__ CUtensorMap map_gath1, const __grid_constant__ CUtensorMap map_b, AgGemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  const Pipe p = carve_smem(smem_raw);
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  FusedPage* page = g.pages[g.rank];
+  const unsigned long long epoch = page->ag_epoch + 1;
+  const int parity = static_cast<int>(epoch & 1ull);
+  const int blocks_per_rank = g.rows_per_rank / BM;
+
+  if (static_cast<int>(blockIdx.x) < g.comm_ctas) {
+    // ------------------------------------------------------------------ comm CTAs: push my shard
+    const size_t block_bytes = static_cast<size_t>(BM) * g.K * 2;
+    const size_t vecs = block_bytes / 16;
+    const size_t per_cta = (vecs + g.comm_ctas - 1) / g.comm_ctas;
+    const size_t v0 = min(vecs, per_cta * blockIdx.x), v1 = min(vecs, v0 + per_cta);
+    const size_t dst_off = g.gathered_off + static_cast<size_t>(parity) * g.gathered_bytes +
+                           static_cast<size_t>(g.rank) * g.rows_per_rank * g.K * 2;
+    for (int b = 0; b < blocks_per_rank; ++b) {
+      const char* src = static_cast<const char*>(g.x_local) + b * block_bytes;
+      if (g.mc_base != nullptr) {
+        char* dst = g.mc_base + dst_off + b * block_bytes;
+        for (size_t v = v0 + threadIdx.x; v < v1; v += blockDim.x)
+          multimem_st16(dst + v * 16, *reinterpret_cast<const uint4*>(src + v * 16));
+      } else {
+        for (size_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+          const uint4 d = *reinterpret_cast<const uint4*>(src + v * 16);
+          for (int q = 1; q < g.nranks; ++q)
+            *reinterpret_cast<uint4*>(g.heap_bases[(g.rank + q) % g.nranks] + dst_off + b * block_bytes + v * 16) = d;
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        if (atomicAdd(&page->ag_block_count[b], 1u) == static_cast<unsigned int>(g.comm_ctas) - 1u) {
+          page->ag_block_count[b] = 0;
+          __threadfence_system();
+          for (int q = 1; q < g.nranks; ++q)
+            st_release_sys(&g.pages[(g.rank + q) % g.nranks]->ag_flag[g.rank][b], epoch);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ GEMM CTAs
+    init_pipe(p);
+    if (threadIdx.x == 0) {
+      prefetch_tensormap(&map_local);
+      prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) tmem_alloc(p.tmem_slot, kTmemCols);
+    tc_fence_before_sync();
+    asm volatile("bar.sync 1, %0;" ::"r"(kGemmThreads) : "memory");
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *p.tmem_slot;
+
+    const int gemm_ctas = gridDim.x - g.comm_ctas;
+    const int cta = blockIdx.x - g.comm_ctas;
+    const int tiles_n = g.N / BN;
+    const int num_tiles = blocks_per_rank * g.nranks * tiles_n;
+    const int k_blocks = g.K / BK;
+    const int my_tiles = (num_tiles - cta + gemm_ctas - 1) / gemm_ctas;
+    const CUtensorMap* map_gath = parity ? &map_gath1 : &map_gath0;
+
+    if (warp == 0) {
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = cta; tile < num_tiles && ok; tile += gemm_ctas) {
+          const int tn = tile % tiles_n, mb = tile / tiles_n;
+          const int b = mb / g.nranks, src = (g.rank + mb % g.nranks) % g.nranks;
+          const bool local = src == g.rank;
+          if (!local) {
+            if (!wait_flag_ge(&page->ag_flag[src][b], epoch, p.abort_flag)) {
+              gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_FLAG, 0, src * 64 + b);
+              ok = false;
+              break;
+            }
+            fence_proxy_async();       // peer stores (generic proxy) before my TMA reads (async proxy)
+          }
+          const int a_row = local ? b * BM : src * g.rows_per_rank + b * BM;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(&p.empty_bar[stage], phase ^ 1, p.abort_flag)) {
+              gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_EMPTY, 0, stage);
+              ok = false;
+              break;
+            }
+            uint8_t* a_dst = p.stage_base + static_cast<size_t>(stage) * kStageBytes;
+            mbar_expect_tx(&p.full_bar[stage], kStageBytes);
+            tma_load_2d(a_dst, local ? &map_local : map_gath, &p.full_bar[stage], kb * BK, a_row);
+            tma_load_2d(a_dst + kABytes, &map_b, &p.full_bar[stage], kb * BK, tn * BN);
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
+        }
+        if (!ok) drain_loads(p);
+      }
+    } else if (warp == 1) {
+      if (lane == 0) mma_role(p, tmem_base, my_tiles, k_blocks, g.error_words);
+    } else {
+      const int quarter = warp % 4;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      __nv_bfloat16* d = static_cast<__nv_bfloat16*>(g.d);
+      for (int tile = cta; tile < num_tiles; tile += gemm_ctas) {
+        const int tn = tile % tiles_n, mb = tile / tiles_n;
+        const int b = mb / g.nranks, src = (g.rank + mb % g.nranks) % g.nranks;
+        bool ok = mbar_wait(&p.acc_full[acc], acc_phase, p.abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_ACC, 2, acc);
+          break;
+        }
+        tc_fence_after_sync();
+        const size_t row = static_cast<size_t>(src) * g.rows_per_rank + b * BM + quarter * 32 + lane;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+        if (EPI == 0) {
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c, r);
+            tc_wait_ld();
+            uint4* out = reinterpret_cast<uint4*>(d + row * g.ldd + tn * BN + c);
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              out[v] = make_uint4(pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1])),
+                                  pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
+                                  pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
+                                  pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7])));
+          }
+        } else {
+          constexpr int H = BN / 2;
+#pragma unroll 1
+          for (int c = 0; c < H; c += 32) {
+            uint32_t gt[32], up[32];
+            tmem_ld32(taddr + c, gt);
+            tmem_ld32(taddr + H + c, up);
+            tc_wait_ld();
+            uint4* out = reinterpret_cast<uint4*>(d + row * g.ldd + tn * H + c);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float gv = __uint_as_float(gt[8 * v + e]);
+                o[e] = gv / (1.0f + __expf(-gv)) * __uint_as_float(up[8 * v + e]);
+              }
+              out[v] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p.acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+    tc_fence_before_sync();
+    asm volatile("bar.sync 1, %0;" ::"r"(kGemmThreads) : "memory");
+    if (warp == 1) {
+      tc_fence_after_sync();
+      tmem_dealloc(tmem_base, kTmemCols);
+    }
+  }
+  // the last CTA to finish advances the launch epoch of this rank
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&page->ag_done, 1u) == gridDim.x - 1u) {
+      page->ag_done = 0;
+      page->ag_epoch = epoch;
+    }
+  }
+}
+
+// ============================================================ GEMM -> reduce-scatter
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmRsArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  const Pipe p = carve_smem(smem_raw);
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  FusedPage* page = g.pages[g.rank];
+  const unsigned long long epoch = page->rs_epoch + 1;
+  const int parity = static_cast<int>(epoch & 1ull);
+  const int blocks_per_rank = g.rows_per_rank / BM;
+  const int tiles_n = g.N / BN;
+  const int num_tiles = blocks_per_rank * g.nranks * tiles_n;
+  const int k_blocks = g.K / BK;
+  const int cta = blockIdx.x, ctas = gridDim.x;
+  const int my_tiles = (num_tiles - cta + ctas - 1) / ctas;
+  // partial buffer on every rank: [parity][source rank][rows_per_rank][N] bf16
+  const size_t slab_bytes = static_cast<size_t>(g.rows_per_rank) * g.N * 2;
+  const size_t parity_off = g.partial_off + static_cast<size_t>(parity) * g.nranks * slab_bytes;
+
+  init_pipe(p);
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) tmem_alloc(p.tmem_slot, kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *p.tmem_slot;
+
+  // tile order: owner-major starting with rank+1 (own rows last), then row block, then column tile
+  auto decode = [&](int tile, int& owner, int& b, int& tn) {
+    tn = tile % tiles_n;
+    const int mb = tile / tiles_n;
+    b = mb % blocks_per_rank;
+    owner = (g.rank + 1 + mb / blocks_per_rank) % g.nranks;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cta; tile < num_tiles && ok; tile += ctas) {
+        int owner, b, tn;
+        decode(tile, owner, b, tn);
+        const int a_row = owner * g.rows_per_rank + b * BM;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&p.empty_bar[stage], phase ^ 1, p.abort_flag)) {
+            gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_EMPTY, 0, stage);
+            ok = false;
+            break;
+          }
+          uint8_t* a_dst = p.stage_base + static_cast<size_t>(stage) * kStageBytes;
+          mbar_expect_tx(&p.full_bar[stage], kStageBytes);
+          tma_load_2d(a_dst, &map_a, &p.full_bar[stage], kb * BK, a_row);
+          tma_load_2d(a_dst + kABytes, &map_b, &p.full_bar[stage], kb * BK, tn * BN);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) drain_loads(p);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) mma_role(p, tmem_base, my_tiles, k_blocks, g.error_words);
+  } else {
+    const int quarter = warp % 4;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = cta; tile < num_tiles; tile += ctas) {
+      int owner, b, tn;
+      decode(tile, owner, b, tn);
+      bool ok = mbar_wait(&p.acc_full[acc], acc_phase, p.abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_ACC, 2, acc);
+        break;
+      }
+      tc_fence_after_sync();
+      // destination: owner's slab for source = me, local row inside the owner's shard
+      char* slab = g.heap_bases[owner] + parity_off + static_cast<size_t>(g.rank) * slab_bytes;
+      const size_t row = static_cast<size_t>(b) * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c, r);
+        tc_wait_ld();
+        uint4* out = reinterpret_cast<uint4*>(slab + (row * g.N + tn * BN + c) * 2);
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          out[v] = make_uint4(pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1])),
+                              pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
+                              pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
+                              pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7])));
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&p.acc_empty[acc]);
+        // this warp's quarter of the tile is on its way: count it on the owner (4 warps x tiles_n per block)
+        __threadfence_system();
+        red_add_release_sys(&g.pages[owner]->rs_count[g.rank][b], 1ull);
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+
+  // ------------------------------------------------------------------ reduction of my rows
+  // work item = (row block b, 16-byte column vector group); every CTA takes a strided share
+  const unsigned long long want = epoch * 4ull * static_cast<unsigned long long>(tiles_n);
+  const char* my_slabs = g.heap_bases[g.rank] + parity_off;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(g.out);
+  const size_t vec_per_block = static_cast<size_t>(BM) * g.N * 2 / 16;
+  __shared__ int s_ok;
+  for (int b = 0; b < blocks_per_rank; ++b) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      for (int s = 0; s < g.nranks && ok; ++s)
+        if (!wait_flag_ge(&page->rs_count[s][b], want, p.abort_flag)) {
+          gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_FLAG, 3, s * 64 + b);
+          ok = 0;
+        }
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (s_ok == 0) break;
+    const size_t base_v = static_cast<size_t>(b) * vec_per_block;
+    for (size_t v = static_cast<size_t>(cta) * blockDim.x + threadIdx.x; v < vec_per_block; v += static_cast<size_t>(ctas) * blockDim.x) {
+      float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int s = 0; s < g.nranks; ++s) {
+        const uint4 d = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + (base_v + v) * 16);
+        const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc8[2 * e] += __uint_as_float(w[e] << 16);
+          acc8[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+        }
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + (base_v + v) * 16) =
+          make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]), pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&page->rs_done, 1u) == gridDim.x - 1u) {
+      page->rs_done = 0;
+      page->rs_epoch = epoch;
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_ag_gemm(const AgGemmArgs& g, int epilogue, int grid, cudaStream_t stream) {
+  if (g.K % BK != 0 || g.N % BN != 0 || g.rows_per_rank % BM != 0 || g.rows_per_rank / BM > kFusedMaxBlocks ||
+      g.nranks > kFusedMaxRanks || g.comm_ctas < 1 || grid <= g.comm_ctas)
+    return cudaErrorInvalidValue;
+  const uint64_t all_rows = static_cast<uint64_t>(g.rows_per_rank) * g.nranks;
+  CUtensorMap map_local = make_bf16_kmajor_map(g.x_local, g.rows_per_rank, g.K, g.K, BM);
+  const char* gath = g.heap_bases_host[g.rank] + g.gathered_off;
+  CUtensorMap map_g0 = make_bf16_kmajor_map(gath, all_rows, g.K, g.K, BM);
+  CUtensorMap map_g1 = make_bf16_kmajor_map(gath + g.gathered_bytes, all_rows, g.K, g.K, BM);
+  CUtensorMap map_b = make_bf16_kmajor_map(g.b, g.N, g.K, g.ldb, BN);
+  auto launch = [&](auto kernel) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+    if (e != cudaSuccess) return e;
+    kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(map_local, map_g0, map_g1, map_b, g);
+    return cudaGetLastError();
+  };
+  return epilogue == 0 ? launch(ag_gemm_kernel<0>) : launch(ag_gemm_kernel<1>);
+}
+
+cudaError_t launch_gemm_rs(const GemmRsArgs& g, int grid, cudaStream_t stream) {
+  if (g.K % BK != 0 || g.N % BN != 0 || g.rows_per_rank % BM != 0 || g.rows_per_rank / BM > kFusedMaxBlocks ||
+      g.nranks > kFusedMaxRanks || grid < 1)
+    return cudaErrorInvalidValue;
+  CUtensorMap map_a = make_bf16_kmajor_map(g.a, static_cast<uint64_t>(g.rows_per_rank) * g.nranks, g.K, g.lda, BM);
+  CUtensorMap map_b = make_bf16_kmajor_map(g.b, g.N, g.K, g.ldb, BN);
+  cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+  if (e != cudaSuccess) return e;
+  gemm_rs_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(map_a, map_b, g);
+  return cudaGetLastError();
+}
+
+}  // namespace sm100
+}  // namespace msccl

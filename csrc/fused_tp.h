@@ -1,0 +1,57 @@
+// Host API and shared structures of the fused tensor-parallel kernels (see fused_tp.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace msccl {
+namespace sm100 {
+
+constexpr int kFusedMaxRanks = 8;
+constexpr int kFusedMaxBlocks = 64;     // 128-row blocks per rank shard
+
+// One per rank inside its symmetric heap; peers write the flag / counter arrays.
+struct alignas(128) FusedPage {
+  unsigned long long ag_flag[kFusedMaxRanks][kFusedMaxBlocks];    // [source][block] = launch epoch when the block has landed
+  unsigned long long rs_count[kFusedMaxRanks][kFusedMaxBlocks];   // [source][block] += 1 per tile quarter stored
+  unsigned long long ag_epoch, rs_epoch;                           // local: launches completed
+  unsigned int ag_block_count[kFusedMaxBlocks];                    // local: comm CTAs done with a block
+  unsigned int ag_done, rs_done;                                   // local: CTAs of the running launch that finished
+  // MoE dispatch / combine
+  unsigned long long moe_flag[kFusedMaxRanks][4];
+  unsigned long long moe_epoch;
+  unsigned int moe_done, moe_pad;
+};
+
+struct AgGemmArgs {
+  const void* x_local;            // [rows_per_rank, K] bf16, contiguous
+  const void* b;                  // [N, K] bf16
+  void* d;                        // [nranks*rows_per_rank, N or N/2] bf16
+  int rows_per_rank, N, K, ldb, ldd;
+  int rank, nranks, comm_ctas;
+  char* const* heap_bases;        // device array: every rank's heap as mapped here
+  char* heap_bases_host[kFusedMaxRanks];
+  FusedPage* pages[kFusedMaxRanks];
+  char* mc_base;                  // multicast window of the heaps (null: peer stores)
+  size_t gathered_off;            // offset of the gathered buffer [2][nranks*rows_per_rank, K] in every heap
+  size_t gathered_bytes;          // bytes of one parity
+  int* error_words;
+};
+
+struct GemmRsArgs {
+  const void* a;                  // [nranks*rows_per_rank, K] bf16
+  const void* b;                  // [N, K] bf16
+  void* out;                      // [rows_per_rank, N] bf16: this rank's reduced rows
+  int rows_per_rank, N, K, lda, ldb;
+  int rank, nranks;
+  char* const* heap_bases;
+  FusedPage* pages[kFusedMaxRanks];
+  size_t partial_off;             // offset of the partial buffer [2][nranks][rows_per_rank, N] in every heap
+  int* error_words;
+};
+
+cudaError_t launch_ag_gemm(const AgGemmArgs& args, int epilogue, int grid, cudaStream_t stream);
+cudaError_t launch_gemm_rs(const GemmRsArgs& args, int grid, cudaStream_t stream);
+
+}  // namespace sm100
+}  // namespace msccl

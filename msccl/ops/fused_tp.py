@@ -1,0 +1,65 @@
+"""Fused tensor-parallel GEMMs: all-gather -> GEMM (optionally with SwiGLU) and GEMM -> reduce-scatter,
+each as ONE sm_100a kernel that overlaps NVLink traffic with tcgen05 tiles (``csrc/fused_tp.cu``).
+
+Sequence-parallel convention: activations enter and leave sharded by tokens
+(``[tokens_per_rank, hidden]`` per rank); weights are sharded along the FFN dimension.
+"""
+import torch
+
+from msccl.ops.gemm import _errors
+from msccl.runtime.comm import Communicator
+
+
+class FusedTensorParallel:
+    """Holds the symmetric buffers of the two fused kernels for fixed shapes."""
+
+    def __init__(self, comm: Communicator, tokens_per_rank: int, hidden: int, comm_ctas: int = 16):
+        if comm.emulated_mode:
+            raise ValueError('the fused kernels need one process per GPU')
+        if tokens_per_rank % 128 or hidden % 256:
+            raise ValueError('tokens_per_rank must be a multiple of 128 and hidden a multiple of 256')
+        self.comm = comm
+        self.n = comm.world
+        self.rows = tokens_per_rank
+        self.hidden = hidden
+        self.comm_ctas = comm_ctas
+        all_rows = self.n * tokens_per_rank
+        self.gathered_bytes = all_rows * hidden * 2
+        _, self.gathered_off = comm.symmetric_empty(2 * all_rows * hidden, torch.bfloat16)
+        _, self.partial_off = comm.symmetric_empty(2 * self.n * tokens_per_rank * hidden, torch.bfloat16)
+        self.sms = comm.native.sm_count()
+        self.launches = 0
+
+    def all_gather_gemm(self, x_local, weight, epilogue='none', out=None, stream=None):
+        """``epilogue(gather(x_local) @ weight.T)``: x_local [rows, hidden], weight [N, hidden] -> [n*rows, N (or N/2)]."""
+        c = self.comm
+        assert x_local.shape == (self.rows, self.hidden) and x_local.is_contiguous() and x_local.dtype == torch.bfloat16
+        n_out, k = weight.shape
+        assert k == self.hidden and weight.stride(1) == 1 and n_out % 256 == 0
+        swiglu = epilogue == 'swiglu'
+        cols = n_out // 2 if swiglu else n_out
+        if out is None:
+            out = torch.empty(self.n * self.rows, cols, dtype=torch.bfloat16, device=x_local.device)
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        c.native.ag_gemm(x_local.data_ptr(), weight.data_ptr(), out.data_ptr(), self.rows, n_out, k, weight.stride(0),
+                         out.stride(0), c.rank, self.n, self.comm_ctas, c.dev_heap_bases, list(c.heap_ptrs), c.off_fused,
+                         c.mc_base, self.gathered_off, self.gathered_bytes, _errors(x_local.device).data_ptr(),
+                         1 if swiglu else 0, self.sms, stream_h)
+        self.launches += 1
+        return out
+
+    def gemm_reduce_scatter(self, a, weight, out=None, stream=None):
+        """``reduce_scatter(a @ weight.T)``: a [n*rows, K_shard], weight [hidden, K_shard] -> this rank's [rows, hidden]."""
+        c = self.comm
+        m, k = a.shape
+        assert m == self.n * self.rows and a.stride(1) == 1 and a.dtype == torch.bfloat16
+        assert weight.shape == (self.hidden, k) and weight.stride(1) == 1 and k % 64 == 0
+        if out is None:
+            out = torch.empty(self.rows, self.hidden, dtype=torch.bfloat16, device=a.device)
+        assert out.is_contiguous()
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        c.native.gemm_rs(a.data_ptr(), weight.data_ptr(), out.data_ptr(), self.rows, self.hidden, k, a.stride(0),
+                         weight.stride(0), c.rank, self.n, c.dev_heap_bases, list(c.heap_ptrs), c.off_fused, self.partial_off,
+                         _errors(a.device).data_ptr(), self.sms, stream_h)
+        self.launches += 1
+        return out

@@ -2,7 +2,7 @@
 
 Heap layout of every rank (identical offsets on all ranks)::
 
-    [ sync page | LL staging (2 x nranks slots) | FIFO area | arena for symmetric user tensors ]
+    [ sync page | fused-kernel flag page | LL staging (2 x nranks slots) | FIFO area | arena for symmetric tensors ]
 
 Two ways to build one:
 
@@ -61,7 +61,8 @@ class Communicator:
     # ------------------------------------------------------------------ layout
     def _set_layout(self, world, ll_max_bytes, fifo_bytes, arena_bytes):
         self.ll_slot_bytes = _align(2 * ll_max_bytes, 1024)
-        self.off_staging = SYNC_BYTES
+        self.off_fused = SYNC_BYTES
+        self.off_staging = 2 * SYNC_BYTES
         self.off_fifo = _align(self.off_staging + 2 * world * self.ll_slot_bytes, 1 << 16)
         self.fifo_bytes = fifo_bytes
         self.off_arena = _align(self.off_fifo + fifo_bytes, 1 << 21)
@@ -71,6 +72,9 @@ class Communicator:
 
     def sync_ptr(self, r):
         return self.heap_ptrs[r]
+
+    def fused_ptr(self, r):
+        return self.heap_ptrs[r] + self.off_fused
 
     def staging_ptr(self, r):
         return self.heap_ptrs[r] + self.off_staging
