@@ -39,14 +39,14 @@ constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 2 * BN;
 constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + 256;
-constexpr unsigned int kFlagSpin = 1u << 26;
+constexpr unsigned long long kFlagTimeoutNs = 5ull * 1000 * 1000 * 1000;   // per wait on a peer
 
 __device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag, unsigned long long want, volatile int* abort_flag) {
-  for (unsigned int i = 0; i < kFlagSpin; ++i) {
+  const unsigned long long deadline = global_timer_ns() + kFlagTimeoutNs;
+  for (unsigned int i = 0;; ++i) {
     if (ld_acquire_sys(flag) >= want) return true;
-    if ((i & 1023u) == 1023u && *abort_flag != 0) return false;
+    if ((i & 255u) == 255u && (*abort_flag != 0 || global_timer_ns() > deadline)) return false;
   }
-  return false;
 }
 
 __device__ __forceinline__ void multimem_st16(void* p, uint4 v) {
@@ -138,6 +138,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
   const Pipe p = carve_smem(smem_raw);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   FusedPage* page = g.pages[g.rank];
+  if (g.error_words != nullptr && *reinterpret_cast<volatile int*>(g.error_words) != 0) return;   // an earlier launch gave up
   const unsigned long long epoch = page->ag_epoch + 1;
   const int parity = static_cast<int>(epoch & 1ull);
   const int blocks_per_rank = g.rows_per_rank / BM;
@@ -313,6 +314,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const Pipe p = carve_smem(smem_raw);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   FusedPage* page = g.pages[g.rank];
+  if (g.error_words != nullptr && *reinterpret_cast<volatile int*>(g.error_words) != 0) return;   // an earlier launch gave up
   const unsigned long long epoch = page->rs_epoch + 1;
   const int parity = static_cast<int>(epoch & 1ull);
   const int blocks_per_rank = g.rows_per_rank / BM;
@@ -421,7 +423,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // ------------------------------------------------------------------ reduction of my rows
   // work item = (row block b, 16-byte column vector group); every CTA takes a strided share
-  const unsigned long long want = epoch * 4ull * static_cast<unsigned long long>(tiles_n);
+  // every source adds 4 * tiles_n to the counter of each of my row blocks per launch (one per
+  // epilogue warp and column tile); the counters are never reset, rs_base remembers where the
+  // previous launch left them
+  const unsigned long long per_launch = 4ull * static_cast<unsigned long long>(tiles_n);
   const char* my_slabs = g.heap_bases[g.rank] + parity_off;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(g.out);
   const size_t vec_per_block = static_cast<size_t>(BM) * g.N * 2 / 16;
@@ -430,7 +435,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0) {
       int ok = 1;
       for (int s = 0; s < g.nranks && ok; ++s)
-        if (!wait_flag_ge(&page->rs_count[s][b], want, p.abort_flag)) {
+        if (!wait_flag_ge(&page->rs_count[s][b], page->rs_base[s][b] + per_launch, p.abort_flag)) {
           gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_FLAG, 3, s * 64 + b);
           ok = 0;
         }
@@ -458,6 +463,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(&page->rs_done, 1u) == gridDim.x - 1u) {
+      for (int s = 0; s < g.nranks; ++s)
+        for (int b = 0; b < blocks_per_rank; ++b) page->rs_base[s][b] += per_launch;
       page->rs_done = 0;
       page->rs_epoch = epoch;
     }

@@ -14,6 +14,7 @@ constexpr int kFusedMaxBlocks = 64;     // 128-row blocks per rank shard
 struct alignas(128) FusedPage {
   unsigned long long ag_flag[kFusedMaxRanks][kFusedMaxBlocks];    // [source][block] = launch epoch when the block has landed
   unsigned long long rs_count[kFusedMaxRanks][kFusedMaxBlocks];   // [source][block] += 1 per tile quarter stored
+  unsigned long long rs_base[kFusedMaxRanks][kFusedMaxBlocks];    // local: rs_count at the end of the previous launch
   unsigned long long ag_epoch, rs_epoch;                           // local: launches completed
   unsigned int ag_block_count[kFusedMaxBlocks];                    // local: comm CTAs done with a block
   unsigned int ag_done, rs_done;                                   // local: CTAs of the running launch that finished

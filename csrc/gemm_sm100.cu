@@ -44,6 +44,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S::kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  if (error_words != nullptr && *reinterpret_cast<volatile int*>(error_words) != 0) return;   // an earlier launch gave up
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = N / BN;
   const int num_tiles = tiles_m * tiles_n;

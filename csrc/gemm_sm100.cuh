@@ -26,7 +26,7 @@ constexpr int BM = 128;           // tile rows  (= TMEM lanes, one tcgen05.mma M
 constexpr int BK = 64;            // 64 bf16 = 128 bytes = one swizzle atom row
 constexpr int UMMA_K = 16;        // K per tcgen05.mma for 16-bit inputs
 constexpr int kGemmThreads = 192;
-constexpr uint32_t kSpinLimit = 1u << 24;   // try_wait attempts before giving up (each may suspend briefly)
+constexpr unsigned long long kMbarTimeoutNs = 10ull * 1000 * 1000 * 1000;   // longest wait on one mbarrier
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -51,11 +51,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait; false = gave up (or another role already failed).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long now;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+  const unsigned long long deadline = now + kMbarTimeoutNs;
+  for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag != 0) return false;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag != 0) return false;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (now > deadline) return false;
+    }
   }
-  return false;
 }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
