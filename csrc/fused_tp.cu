@@ -153,15 +153,30 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
                            static_cast<size_t>(g.rank) * g.rows_per_rank * g.K * 2;
     for (int b = 0; b < blocks_per_rank; ++b) {
       const char* src = static_cast<const char*>(g.x_local) + b * block_bytes;
-      if (g.mc_base != nullptr) {
-        char* dst = g.mc_base + dst_off + b * block_bytes;
-        for (size_t v = v0 + threadIdx.x; v < v1; v += blockDim.x)
-          multimem_st16(dst + v * 16, *reinterpret_cast<const uint4*>(src + v * 16));
-      } else {
-        for (size_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-          const uint4 d = *reinterpret_cast<const uint4*>(src + v * 16);
-          for (int q = 1; q < g.nranks; ++q)
-            *reinterpret_cast<uint4*>(g.heap_bases[(g.rank + q) % g.nranks] + dst_off + b * block_bytes + v * 16) = d;
+      constexpr int U = 8;
+      for (size_t base = v0 + threadIdx.x; base < v1; base += static_cast<size_t>(blockDim.x) * U) {
+        uint4 d[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const size_t v = base + static_cast<size_t>(u) * blockDim.x;
+          if (v < v1) d[u] = *reinterpret_cast<const uint4*>(src + v * 16);
+        }
+        if (g.mc_base != nullptr) {
+          char* dst = g.mc_base + dst_off + b * block_bytes;
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const size_t v = base + static_cast<size_t>(u) * blockDim.x;
+            if (v < v1) multimem_st16(dst + v * 16, d[u]);
+          }
+        } else {
+          for (int q = 1; q < g.nranks; ++q) {
+            char* dst = g.heap_bases[(g.rank + q) % g.nranks] + dst_off + b * block_bytes;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const size_t v = base + static_cast<size_t>(u) * blockDim.x;
+              if (v < v1) *reinterpret_cast<uint4*>(dst + v * 16) = d[u];
+            }
+          }
         }
       }
       __syncthreads();
@@ -376,6 +391,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int quarter = warp % 4;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int cur_owner = -1, tiles_for_owner = 0;
     for (int tile = cta; tile < num_tiles; tile += ctas) {
       int owner, b, tn;
       decode(tile, owner, b, tn);
@@ -387,31 +403,47 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       tc_fence_after_sync();
       // destination: owner's slab for source = me, local row inside the owner's shard
+      if (owner != cur_owner) {
+        // all tiles of the previous owner are stored: make them visible there, then count them
+        if (cur_owner >= 0 && lane == 0) {
+          __threadfence_system();
+          red_add_release_sys(&g.pages[cur_owner]->rs_count[g.rank][0], static_cast<unsigned long long>(tiles_for_owner));
+        }
+        cur_owner = owner;
+        tiles_for_owner = 0;
+      }
       char* slab = g.heap_bases[owner] + parity_off + static_cast<size_t>(g.rank) * slab_bytes;
       const size_t row = static_cast<size_t>(b) * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c, r);
+      for (int c = 0; c < BN; c += 64) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(taddr + c, r0);
+        tmem_ld32(taddr + c + 32, r1);
         tc_wait_ld();
-        uint4* out = reinterpret_cast<uint4*>(slab + (row * g.N + tn * BN + c) * 2);
+        uint4* out = reinterpret_cast<uint4*>(slab + (row * g.N + tn * BN + c) * 2);   // 128 contiguous bytes
 #pragma unroll
         for (int v = 0; v < 4; ++v)
-          out[v] = make_uint4(pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1])),
-                              pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
-                              pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
-                              pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7])));
+          out[v] = make_uint4(pack_bf16(__uint_as_float(r0[8 * v + 0]), __uint_as_float(r0[8 * v + 1])),
+                              pack_bf16(__uint_as_float(r0[8 * v + 2]), __uint_as_float(r0[8 * v + 3])),
+                              pack_bf16(__uint_as_float(r0[8 * v + 4]), __uint_as_float(r0[8 * v + 5])),
+                              pack_bf16(__uint_as_float(r0[8 * v + 6]), __uint_as_float(r0[8 * v + 7])));
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          out[4 + v] = make_uint4(pack_bf16(__uint_as_float(r1[8 * v + 0]), __uint_as_float(r1[8 * v + 1])),
+                                  pack_bf16(__uint_as_float(r1[8 * v + 2]), __uint_as_float(r1[8 * v + 3])),
+                                  pack_bf16(__uint_as_float(r1[8 * v + 4]), __uint_as_float(r1[8 * v + 5])),
+                                  pack_bf16(__uint_as_float(r1[8 * v + 6]), __uint_as_float(r1[8 * v + 7])));
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&p.acc_empty[acc]);
-        // this warp's quarter of the tile is on its way: count it on the owner (4 warps x tiles_n per block)
-        __threadfence_system();
-        red_add_release_sys(&g.pages[owner]->rs_count[g.rank][b], 1ull);
-      }
+      if (lane == 0) mbar_arrive(&p.acc_empty[acc]);
+      ++tiles_for_owner;
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (cur_owner >= 0 && lane == 0) {
+      __threadfence_system();
+      red_add_release_sys(&g.pages[cur_owner]->rs_count[g.rank][0], static_cast<unsigned long long>(tiles_for_owner));
     }
   }
   tc_fence_before_sync();
@@ -423,48 +455,51 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // ------------------------------------------------------------------ reduction of my rows
   // work item = (row block b, 16-byte column vector group); every CTA takes a strided share
-  // every source adds 4 * tiles_n to the counter of each of my row blocks per launch (one per
-  // epilogue warp and column tile); the counters are never reset, rs_base remembers where the
-  // previous launch left them
-  const unsigned long long per_launch = 4ull * static_cast<unsigned long long>(tiles_n);
+  // Every source adds one count per (epilogue warp, tile) it stored into my slab: 4 * tiles_n *
+  // blocks_per_rank per launch.  The counters are never reset; rs_base remembers where the
+  // previous launch left them.
+  const unsigned long long per_launch = 4ull * static_cast<unsigned long long>(tiles_n) * blocks_per_rank;
   const char* my_slabs = g.heap_bases[g.rank] + parity_off;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(g.out);
-  const size_t vec_per_block = static_cast<size_t>(BM) * g.N * 2 / 16;
+  const size_t total_vecs = static_cast<size_t>(g.rows_per_rank) * g.N * 2 / 16;
   __shared__ int s_ok;
-  for (int b = 0; b < blocks_per_rank; ++b) {
-    if (threadIdx.x == 0) {
-      int ok = 1;
-      for (int s = 0; s < g.nranks && ok; ++s)
-        if (!wait_flag_ge(&page->rs_count[s][b], page->rs_base[s][b] + per_launch, p.abort_flag)) {
-          gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_FLAG, 3, s * 64 + b);
-          ok = 0;
-        }
-      s_ok = ok;
-    }
-    __syncthreads();
-    if (s_ok == 0) break;
-    const size_t base_v = static_cast<size_t>(b) * vec_per_block;
-    for (size_t v = static_cast<size_t>(cta) * blockDim.x + threadIdx.x; v < vec_per_block; v += static_cast<size_t>(ctas) * blockDim.x) {
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int s = 0; s < g.nranks && ok; ++s)
+      if (!wait_flag_ge(&page->rs_count[s][0], page->rs_base[s][0] + per_launch, p.abort_flag)) {
+        gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_FLAG, 3, s);
+        ok = 0;
+      }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (s_ok != 0) {
+    for (size_t v = static_cast<size_t>(cta) * blockDim.x + threadIdx.x; v < total_vecs; v += static_cast<size_t>(ctas) * blockDim.x) {
       float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int s = 0; s < g.nranks; ++s) {
-        const uint4 d = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + (base_v + v) * 16);
-        const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+      uint4 part[kFusedMaxRanks];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          acc8[2 * e] += __uint_as_float(w[e] << 16);
-          acc8[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+      for (int s = 0; s < kFusedMaxRanks; ++s)        // all loads in flight before the first add
+        if (s < g.nranks) part[s] = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + v * 16);
+#pragma unroll
+      for (int s = 0; s < kFusedMaxRanks; ++s) {
+        if (s < g.nranks) {
+          const uint32_t w[4] = {part[s].x, part[s].y, part[s].z, part[s].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc8[2 * e] += __uint_as_float(w[e] << 16);
+            acc8[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+          }
         }
       }
-      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + (base_v + v) * 16) =
+      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + v * 16) =
           make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]), pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
     }
-    __syncthreads();
   }
+  __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(&page->rs_done, 1u) == gridDim.x - 1u) {
-      for (int s = 0; s < g.nranks; ++s)
-        for (int b = 0; b < blocks_per_rank; ++b) page->rs_base[s][b] += per_launch;
+      for (int s = 0; s < g.nranks; ++s) page->rs_base[s][0] += per_launch;
       page->rs_done = 0;
       page->rs_epoch = epoch;
     }
