@@ -222,14 +222,14 @@ PYBIND11_MODULE(_msccl_native, m) {
   m.def("ag_gemm", [](uintptr_t x_local, uintptr_t b, uintptr_t d, int rows_per_rank, int N, int K, int ldb, int ldd, int rank,
                        int nranks, int comm_ctas, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs, size_t off_fused,
                        uintptr_t mc_base, size_t gathered_off, size_t gathered_bytes, uintptr_t error_words, int epilogue,
-                       int grid, uintptr_t stream) {
+                       int grid, int tuning, uintptr_t stream) {
     msccl::sm100::AgGemmArgs g;
     std::memset(&g, 0, sizeof(g));
     g.x_local = reinterpret_cast<const void*>(x_local);
     g.b = reinterpret_cast<const void*>(b);
     g.d = reinterpret_cast<void*>(d);
     g.rows_per_rank = rows_per_rank; g.N = N; g.K = K; g.ldb = ldb; g.ldd = ldd;
-    g.rank = rank; g.nranks = nranks; g.comm_ctas = comm_ctas;
+    g.rank = rank; g.nranks = nranks; g.comm_ctas = comm_ctas; g.tuning = tuning;
     g.heap_bases = reinterpret_cast<char* const*>(heap_bases_dev);
     if (static_cast<int>(heap_ptrs.size()) != nranks || nranks > msccl::sm100::kFusedMaxRanks) throw std::runtime_error("bad rank count");
     for (int r = 0; r < nranks; ++r) {

@@ -134,11 +134,30 @@ twoshot_allreduce_kernel(char* const* heap_bases, char* mc, long long offset, lo
       }
     }
   } else {
-    for (long long v = begin + threadIdx.x; v < end; v += blockDim.x) {
-      uint4 acc = *reinterpret_cast<const uint4*>(heap_bases[0] + offset + v * 16);
-      for (int r = 1; r < nranks; ++r)
-        acc = Vec16<T>::add(acc, *reinterpret_cast<const uint4*>(heap_bases[r] + offset + v * 16));
-      for (int r = 0; r < nranks; ++r) *reinterpret_cast<uint4*>(heap_bases[(rank + r) % nranks] + offset + v * 16) = acc;
+    // peer loads: all n loads of two vectors are issued before the first add, sums in rank order
+    constexpr int PU = 2;
+    for (long long v = begin + threadIdx.x; v < end; v += static_cast<long long>(blockDim.x) * PU) {
+      constexpr int R8 = 8;       // ranks loaded together; a box has at most 8 GPUs, more are summed in a tail loop
+      uint4 part[PU][R8];
+#pragma unroll
+      for (int u = 0; u < PU; ++u) {
+        const long long i = v + static_cast<long long>(u) * blockDim.x;
+#pragma unroll
+        for (int r = 0; r < R8; ++r)
+          if (r < nranks && i < end) part[u][r] = *reinterpret_cast<const uint4*>(heap_bases[r] + offset + i * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < PU; ++u) {
+        const long long i = v + static_cast<long long>(u) * blockDim.x;
+        if (i >= end) break;
+        uint4 acc = part[u][0];
+#pragma unroll
+        for (int r = 1; r < R8; ++r)
+          if (r < nranks) acc = Vec16<T>::add(acc, part[u][r]);
+        for (int r = R8; r < nranks; ++r)
+          acc = Vec16<T>::add(acc, *reinterpret_cast<const uint4*>(heap_bases[r] + offset + i * 16));
+        for (int r = 0; r < nranks; ++r) *reinterpret_cast<uint4*>(heap_bases[(rank + r) % nranks] + offset + i * 16) = acc;
+      }
     }
   }
   rank_barrier(syncs, rank, nranks, deadline, &s_fail);               // every slice has been published

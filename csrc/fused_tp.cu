@@ -129,6 +129,24 @@ __device__ __forceinline__ void drain_loads(const Pipe& p) {
     for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&p.full_bar[s], 0) && !mbar_try_wait(&p.full_bar[s], 1); ++i) {}
 }
 
+// Tile -> (column tile, row block).  Row blocks are numbered in arrival order (block-major over
+// sources).  Default: column tile fastest (CTAs running together share a row block of A).
+// tuning bit 0: groups of 8 row blocks with the row block fastest inside a group, which makes CTAs
+// running together share column tiles of B instead.
+__device__ __forceinline__ void ag_decode(int tile, int tiles_n, int row_blocks, int tuning, int& tn, int& mb) {
+  if ((tuning & 1) == 0) {
+    tn = tile % tiles_n;
+    mb = tile / tiles_n;
+  } else {
+    constexpr int G = 8;
+    const int per_group = G * tiles_n;
+    const int group = tile / per_group, in_group = tile % per_group;
+    const int rows_here = min(G, row_blocks - group * G);
+    mb = group * G + in_group % rows_here;
+    tn = in_group / rows_here;
+  }
+}
+
 // ============================================================ all-gather -> GEMM (+SwiGLU)
 template <int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -153,7 +171,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
                            static_cast<size_t>(g.rank) * g.rows_per_rank * g.K * 2;
     for (int b = 0; b < blocks_per_rank; ++b) {
       const char* src = static_cast<const char*>(g.x_local) + b * block_bytes;
-      constexpr int U = 8;
+      constexpr int U = 16;       // 256 bytes per thread in flight: the copy is latency bound otherwise
       for (size_t base = v0 + threadIdx.x; base < v1; base += static_cast<size_t>(blockDim.x) * U) {
         uint4 d[U];
 #pragma unroll
@@ -209,7 +227,6 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
     const int num_tiles = blocks_per_rank * g.nranks * tiles_n;
     const int k_blocks = g.K / BK;
     const int my_tiles = (num_tiles - cta + gemm_ctas - 1) / gemm_ctas;
-    const CUtensorMap* map_gath = parity ? &map_gath1 : &map_gath0;
 
     if (warp == 0) {
       if (lane == 0) {
@@ -217,7 +234,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
         uint32_t phase = 0;
         bool ok = true;
         for (int tile = cta; tile < num_tiles && ok; tile += gemm_ctas) {
-          const int tn = tile % tiles_n, mb = tile / tiles_n;
+          int tn, mb;
+          ag_decode(tile, tiles_n, blocks_per_rank * g.nranks, g.tuning, tn, mb);
           const int b = mb / g.nranks, src = (g.rank + mb % g.nranks) % g.nranks;
           const bool local = src == g.rank;
           if (!local) {
@@ -237,7 +255,9 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
             }
             uint8_t* a_dst = p.stage_base + static_cast<size_t>(stage) * kStageBytes;
             mbar_expect_tx(&p.full_bar[stage], kStageBytes);
-            tma_load_2d(a_dst, local ? &map_local : map_gath, &p.full_bar[stage], kb * BK, a_row);
+            if (local) tma_load_2d(a_dst, &map_local, &p.full_bar[stage], kb * BK, a_row);
+            else if (parity) tma_load_2d(a_dst, &map_gath1, &p.full_bar[stage], kb * BK, a_row);
+            else tma_load_2d(a_dst, &map_gath0, &p.full_bar[stage], kb * BK, a_row);
             tma_load_2d(a_dst + kABytes, &map_b, &p.full_bar[stage], kb * BK, tn * BN);
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
@@ -252,7 +272,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
       uint32_t acc_phase = 0;
       __nv_bfloat16* d = static_cast<__nv_bfloat16*>(g.d);
       for (int tile = cta; tile < num_tiles; tile += gemm_ctas) {
-        const int tn = tile % tiles_n, mb = tile / tiles_n;
+        int tn, mb;
+        ag_decode(tile, tiles_n, blocks_per_rank * g.nranks, g.tuning, tn, mb);
         const int b = mb / g.nranks, src = (g.rank + mb % g.nranks) % g.nranks;
         bool ok = mbar_wait(&p.acc_full[acc], acc_phase, p.abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -474,25 +495,36 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   __syncthreads();
   if (s_ok != 0) {
-    for (size_t v = static_cast<size_t>(cta) * blockDim.x + threadIdx.x; v < total_vecs; v += static_cast<size_t>(ctas) * blockDim.x) {
-      float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      uint4 part[kFusedMaxRanks];
+    constexpr int RU = 4;          // vectors per thread per pass; with 8 sources that is 32 loads in flight
+    const size_t stride = static_cast<size_t>(ctas) * blockDim.x;
+    for (size_t v = static_cast<size_t>(cta) * blockDim.x + threadIdx.x; v < total_vecs; v += stride * RU) {
+      uint4 part[RU][kFusedMaxRanks];
 #pragma unroll
-      for (int s = 0; s < kFusedMaxRanks; ++s)        // all loads in flight before the first add
-        if (s < g.nranks) part[s] = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + v * 16);
+      for (int u = 0; u < RU; ++u) {
+        const size_t vv = v + u * stride;
 #pragma unroll
-      for (int s = 0; s < kFusedMaxRanks; ++s) {
-        if (s < g.nranks) {
-          const uint32_t w[4] = {part[s].x, part[s].y, part[s].z, part[s].w};
+        for (int s = 0; s < kFusedMaxRanks; ++s)
+          if (s < g.nranks && vv < total_vecs) part[u][s] = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + vv * 16);
+      }
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            acc8[2 * e] += __uint_as_float(w[e] << 16);
-            acc8[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+      for (int u = 0; u < RU; ++u) {
+        const size_t vv = v + u * stride;
+        if (vv >= total_vecs) break;
+        float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int s = 0; s < kFusedMaxRanks; ++s) {
+          if (s < g.nranks) {
+            const uint32_t w[4] = {part[u][s].x, part[u][s].y, part[u][s].z, part[u][s].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              acc8[2 * e] += __uint_as_float(w[e] << 16);
+              acc8[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+            }
           }
         }
+        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + vv * 16) =
+            make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]), pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
       }
-      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + v * 16) =
-          make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]), pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
     }
   }
   __syncthreads();

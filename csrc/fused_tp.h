@@ -30,6 +30,7 @@ struct AgGemmArgs {
   void* d;                        // [nranks*rows_per_rank, N or N/2] bf16
   int rows_per_rank, N, K, ldb, ldd;
   int rank, nranks, comm_ctas;
+  int tuning;                     // bit 0: order tiles row-block-fastest inside a (block, source) wave group
   char* const* heap_bases;        // device array: every rank's heap as mapped here
   char* heap_bases_host[kFusedMaxRanks];
   FusedPage* pages[kFusedMaxRanks];

@@ -4,6 +4,8 @@ each as ONE sm_100a kernel that overlaps NVLink traffic with tcgen05 tiles (``cs
 Sequence-parallel convention: activations enter and leave sharded by tokens
 (``[tokens_per_rank, hidden]`` per rank); weights are sharded along the FFN dimension.
 """
+import os
+
 import torch
 
 from msccl.ops.gemm import _errors
@@ -29,6 +31,8 @@ class FusedTensorParallel:
         _, self.partial_off = comm.symmetric_empty(2 * self.n * tokens_per_rank * hidden, torch.bfloat16)
         self.sms = comm.native.sm_count()
         self.launches = 0
+        self.tuning = int(os.environ.get('MSCCL_AG_TUNING', '0'))
+        self.grid = int(os.environ.get('MSCCL_AG_GRID', '0'))
 
     def all_gather_gemm(self, x_local, weight, epilogue='none', out=None, stream=None):
         """``epilogue(gather(x_local) @ weight.T)``: x_local [rows, hidden], weight [N, hidden] -> [n*rows, N (or N/2)]."""
@@ -44,7 +48,7 @@ class FusedTensorParallel:
         c.native.ag_gemm(x_local.data_ptr(), weight.data_ptr(), out.data_ptr(), self.rows, n_out, k, weight.stride(0),
                          out.stride(0), c.rank, self.n, self.comm_ctas, c.dev_heap_bases, list(c.heap_ptrs), c.off_fused,
                          c.mc_base, self.gathered_off, self.gathered_bytes, _errors(x_local.device).data_ptr(),
-                         1 if swiglu else 0, self.sms, stream_h)
+                         1 if swiglu else 0, self.grid or self.sms, self.tuning, stream_h)
         self.launches += 1
         return out
 

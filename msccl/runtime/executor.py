@@ -191,7 +191,9 @@ class Executor:
             if offset is None:
                 raise PlanError('two-shot all-reduce needs a tensor from Communicator.symmetric_empty')
             ctas = int(os.environ.get('MSCCL_TWOSHOT_CTAS', '0')) or max(1, min(128, nbytes // (128 << 10) or 1))
-            comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, offset, nbytes, code, comm.rank,
+            # in-switch reduction pays off from 4 ranks up; with 2 ranks plain peer loads are faster
+            use_nvls = comm.mc_base and os.environ.get('MSCCL_TWOSHOT_NVLS', '1' if comm.world > 2 else '0') == '1'
+            comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base if use_nvls else 0, offset, nbytes, code, comm.rank,
                                           comm.world, comm.dev_syncs, comm.timeout_ns, ctas, stream_h)
             self.launches += 1
             return tensor
