@@ -14,6 +14,7 @@
 
 #include "fused_tp.h"
 #include "gemm_sm100.h"
+#include "moe_a2a.h"
 #include "msccl_device.h"
 #include "symm_mem.h"
 
@@ -261,6 +262,39 @@ PYBIND11_MODULE(_msccl_native, m) {
     check_rt(msccl::sm100::launch_gemm_rs(g, grid, as_stream(stream)), "launch of the fused GEMM reduce-scatter kernel");
   });
   m.def("sm_count", &msccl::sm100::sm_count);
+  // Fused MoE: phase 0 = dispatch + grouped gate/up GEMM (SwiGLU), phase 1 = grouped down GEMM + combine.
+  // geom = [rank, nranks, tokens, topk, hidden, ffn, num_experts, local_experts, cap, comm_ctas]
+  // layout = [counts_off, meta_off, dispatch_off, combine_off, counts_parity, meta_parity, dispatch_parity, combine_parity]
+  m.def("moe_phase", [](int phase, std::vector<int> geom, std::vector<size_t> layout, uintptr_t heap_bases_dev,
+                         std::vector<uintptr_t> heap_ptrs, size_t off_fused, size_t moe_off, uintptr_t x, uintptr_t sorted_copy,
+                         uintptr_t expert_start, uintptr_t copy_weight, uintptr_t w_gate_up, uintptr_t h, uintptr_t w_down,
+                         uintptr_t y, uintptr_t error_words, int grid, uintptr_t stream) {
+    if (geom.size() != 10 || layout.size() != 8) throw std::runtime_error("bad geometry/layout vectors");
+    msccl::sm100::MoeArgs g;
+    std::memset(&g, 0, sizeof(g));
+    g.rank = geom[0]; g.nranks = geom[1]; g.tokens = geom[2]; g.topk = geom[3]; g.hidden = geom[4]; g.ffn = geom[5];
+    g.num_experts = geom[6]; g.local_experts = geom[7]; g.cap = geom[8]; g.comm_ctas = geom[9];
+    if (static_cast<int>(heap_ptrs.size()) != g.nranks || g.nranks > msccl::sm100::kFusedMaxRanks) throw std::runtime_error("bad rank count");
+    g.heap_bases = reinterpret_cast<char* const*>(heap_bases_dev);
+    for (int r = 0; r < g.nranks; ++r) {
+      g.heap_bases_host[r] = reinterpret_cast<char*>(heap_ptrs[r]);
+      g.pages[r] = reinterpret_cast<msccl::sm100::FusedPage*>(heap_ptrs[r] + off_fused);
+    }
+    g.moe_off = moe_off;
+    g.lay.counts_off = layout[0]; g.lay.meta_off = layout[1]; g.lay.dispatch_off = layout[2]; g.lay.combine_off = layout[3];
+    g.lay.counts_parity = layout[4]; g.lay.meta_parity = layout[5]; g.lay.dispatch_parity = layout[6]; g.lay.combine_parity = layout[7];
+    g.x = reinterpret_cast<const void*>(x);
+    g.sorted_copy = reinterpret_cast<const int*>(sorted_copy);
+    g.expert_start = reinterpret_cast<const int*>(expert_start);
+    g.copy_weight = reinterpret_cast<const float*>(copy_weight);
+    g.w_gate_up = reinterpret_cast<const void*>(w_gate_up);
+    g.h = reinterpret_cast<void*>(h);
+    g.w_down = reinterpret_cast<const void*>(w_down);
+    g.y = reinterpret_cast<void*>(y);
+    g.error_words = reinterpret_cast<int*>(error_words);
+    if (phase == 0) check_rt(msccl::sm100::launch_moe_dispatch_gemm(g, grid, as_stream(stream)), "launch of the MoE dispatch kernel");
+    else check_rt(msccl::sm100::launch_moe_gemm_combine(g, grid, as_stream(stream)), "launch of the MoE combine kernel");
+  });
   // In-place all-reduce of `bytes` at `offset` of every rank's symmetric heap.  mc_base = 0
   // selects peer loads/stores, otherwise the NVLink multicast window is used.
   m.def("twoshot_allreduce", [](uintptr_t heap_bases_dev, uintptr_t mc_base, long long offset, long long bytes, int dtype,

@@ -26,3 +26,12 @@ def test_fused_tensor_parallel_kernels():
            '--master-addr', '127.0.0.1', '--master-port', '29621', os.path.join(ROOT, 'tests', 'mp_fused_worker.py')]
     run = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     assert run.returncode == 0 and 'FUSED_TP_OK' in run.stdout, run.stdout[-3000:] + run.stderr[-3000:]
+
+
+def test_fused_moe_kernels():
+    n = torch.cuda.device_count()
+    n = 8 if n >= 8 else (4 if n >= 4 else 2)
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={n}',
+           '--master-addr', '127.0.0.1', '--master-port', '29631', os.path.join(ROOT, 'tests', 'mp_moe_worker.py')]
+    run = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0 and 'FUSED_MOE_OK' in run.stdout, run.stdout[-3000:] + run.stderr[-3000:]
