@@ -1,0 +1,135 @@
+"""``msccl run`` / ``msccl bench``: execute registered plans (or one XML file) with the native executor
+and print one JSON row per size: {collective, algo, nranks, bytes, time_us (max over ranks), algbw, busbw}.
+
+Run under torchrun with one process per GPU, e.g.
+``torchrun --nproc-per-node 8 --master-addr 127.0.0.1 -m msccl bench --collective allreduce --nccl``.
+"""
+import json
+import os
+
+import torch
+
+from msccl.utils.sizes import parse_size
+
+_DTYPES = {'bf16': torch.bfloat16, 'fp16': torch.float16, 'fp32': torch.float32}
+
+
+def _bus_factor(collective, n):
+    if n <= 1:
+        return 1.0
+    return 2.0 * (n - 1) / n if collective == 'allreduce' else (n - 1) / n
+
+
+def _timed(fn, iters, dist):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(b) / iters], device='cuda', dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main_from_args(args, check=False):
+    import torch.distributed as dist
+    import msccl
+    from msccl.runtime import Communicator, Executor
+    from msccl.xml import load_xml_file
+    if 'RANK' not in os.environ:
+        raise SystemExit('msccl run/bench needs one process per GPU: launch it with torchrun '
+                         '(--nproc-per-node N --master-addr 127.0.0.1 -m msccl ...)')
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+    rank, n = dist.get_rank(), dist.get_world_size()
+    dtype = _DTYPES[args.dtype]
+    esize = torch.empty((), dtype=dtype).element_size()
+    lo, hi = parse_size(args.min_bytes), parse_size(args.max_bytes)
+    comm = Communicator.from_process_group(arena_bytes=hi + (8 << 20))
+    ex = Executor(comm)
+    if args.xml is not None:
+        ex.register(load_xml_file(args.xml))
+    else:
+        machine = 'b200' if n == 8 else f'b200x{n}'
+        if rank == 0:
+            msccl.init(machine, 1, (args.collective, (0, None)))
+            path = [os.environ.get('MSCCL_CONFIG')]
+        else:
+            path = [None]
+        dist.broadcast_object_list(path, src=0)
+        if path[0]:
+            ex.load_plan_table(path[0])
+    coll = args.collective
+    size = lo
+    while size <= hi:
+        numel = size // esize // (n * 16) * (n * 16)
+        if numel == 0:
+            size *= 4
+            continue
+        nbytes = numel * esize
+        gen = torch.Generator(device='cuda').manual_seed(1 + rank)
+        if coll == 'allreduce':
+            sym, _ = (comm.tensor_at(comm.rank, comm.off_arena, numel, dtype), 0)
+            src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
+            fn = lambda: ex.all_reduce(sym)                                               # noqa: E731
+            ref_fn = lambda t: dist.all_reduce(t)                                          # noqa: E731
+            algo = 'auto'
+        else:
+            plan = ex.select(coll, nbytes if coll != 'allgather' else nbytes // n)
+            if plan is None:
+                size *= 4
+                continue
+            algo = plan.algo.name
+            if coll == 'allgather':
+                src = torch.randn(numel // n, device='cuda', generator=gen).to(dtype)
+                out = torch.empty(numel, device='cuda', dtype=dtype)
+                ref_fn = lambda t: dist.all_gather_into_tensor(out, t)                    # noqa: E731
+            elif coll == 'reduce_scatter':
+                src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
+                out = torch.empty(numel // n, device='cuda', dtype=dtype)
+                ref_fn = lambda t: dist.reduce_scatter_tensor(out, t)                     # noqa: E731
+            else:
+                src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
+                out = torch.empty(numel, device='cuda', dtype=dtype)
+                ref_fn = lambda t: dist.all_to_all_single(out, t)                         # noqa: E731
+            mine = torch.empty_like(out)
+            fn = lambda: ex.run(plan, src, mine)                                           # noqa: E731
+        if check:
+            if coll == 'allreduce':
+                sym.copy_(src)
+                fn()
+                want = src.clone()
+                ref_fn(want)
+                got = sym
+            else:
+                fn()
+                ref_fn(src)
+                got, want = mine, out
+            ex.check()
+            ok = torch.allclose(got.float(), want.float(), rtol=3e-2, atol=3e-2)
+            if rank == 0:
+                print(json.dumps({'collective': coll, 'algo': algo, 'nranks': n, 'bytes': nbytes, 'matches_nccl': bool(ok)}),
+                      flush=True)
+        else:
+            iters = 50 if nbytes <= (1 << 22) else 10
+            ms = _timed(fn, iters, dist)
+            ex.check()
+            row = {'collective': coll, 'algo': algo, 'nranks': n, 'bytes': nbytes, 'time_us': round(ms * 1e3, 2),
+                   'algbw_gbs': round(nbytes / ms / 1e6, 2), 'busbw_gbs': round(nbytes * _bus_factor(coll, n) / ms / 1e6, 2)}
+            if args.nccl:
+                t = src.clone()
+                nccl_ms = _timed(lambda: ref_fn(t), iters, dist)
+                row['nccl_time_us'] = round(nccl_ms * 1e3, 2)
+                row['nccl_busbw_gbs'] = round(nbytes * _bus_factor(coll, n) / nccl_ms / 1e6, 2)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+        size *= 4
+    comm.close()
+    dist.destroy_process_group()
