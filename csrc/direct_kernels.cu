@@ -191,25 +191,57 @@ oneshot_ll_allreduce_kernel(const void* in, void* out, char* const* staging, lon
       st_volatile_v4(pk + 1, p1);
     }
   }
-  // pull: sum the n slots of my own staging area in rank order
+  // pull: sum the n slots of my own staging area in rank order.  All slots of a vector are polled
+  // together (the loads overlap); only slots whose flags have not arrived yet are read again.
   const char* mine = staging[rank] + parity_off;
   for (long long v = tid; v < vectors; v += nthreads) {
-    uint4 acc;
-    for (int r = 0; r < nranks; ++r) {
-      const uint4* pk = reinterpret_cast<const uint4*>(mine + r * slot_bytes) + 2 * v;
-      uint4 a, b;
-      unsigned int spins = 0;
-      while (true) {
-        a = ld_volatile_v4(pk);
-        b = ld_volatile_v4(pk + 1);
-        if (a.y == flag && a.w == flag && b.y == flag && b.w == flag) break;
-        if ((++spins & 255u) == 0 && (s_fail != 0 || global_timer_ns() > deadline)) {
-          if (atomicExch(&s_fail, 1) == 0) fail_direct(sync, STATUS_TIMEOUT_DATA, rank, r, 0);
-          break;
+    constexpr int R8 = 8;
+    uint4 a[R8], b[R8];
+    unsigned int pending = (nranks >= 32) ? 0xffffffffu : ((1u << nranks) - 1u);
+    unsigned int spins = 0;
+    while (pending != 0 && nranks <= R8) {
+#pragma unroll
+      for (int r = 0; r < R8; ++r) {
+        if (pending & (1u << r)) {
+          const uint4* pk = reinterpret_cast<const uint4*>(mine + r * slot_bytes) + 2 * v;
+          a[r] = ld_volatile_v4(pk);
+          b[r] = ld_volatile_v4(pk + 1);
         }
       }
-      const uint4 d = make_uint4(a.x, a.z, b.x, b.z);
-      acc = (r == 0) ? d : Vec16<T>::add(acc, d);
+#pragma unroll
+      for (int r = 0; r < R8; ++r)
+        if ((pending & (1u << r)) && a[r].y == flag && a[r].w == flag && b[r].y == flag && b[r].w == flag) pending &= ~(1u << r);
+      if (pending != 0 && (++spins & 255u) == 0 && (s_fail != 0 || global_timer_ns() > deadline)) {
+        if (atomicExch(&s_fail, 1) == 0) fail_direct(sync, STATUS_TIMEOUT_DATA, rank, __ffs(pending) - 1, 0);
+        break;
+      }
+    }
+    uint4 acc = make_uint4(0, 0, 0, 0);
+    if (nranks <= R8) {
+#pragma unroll
+      for (int r = 0; r < R8; ++r) {
+        if (r < nranks) {
+          const uint4 d = make_uint4(a[r].x, a[r].z, b[r].x, b[r].z);
+          acc = (r == 0) ? d : Vec16<T>::add(acc, d);
+        }
+      }
+    } else {
+      for (int r = 0; r < nranks; ++r) {       // more than 8 ranks: one slot at a time
+        const uint4* pk = reinterpret_cast<const uint4*>(mine + r * slot_bytes) + 2 * v;
+        uint4 pa, pb;
+        unsigned int sp = 0;
+        while (true) {
+          pa = ld_volatile_v4(pk);
+          pb = ld_volatile_v4(pk + 1);
+          if (pa.y == flag && pa.w == flag && pb.y == flag && pb.w == flag) break;
+          if ((++sp & 255u) == 0 && (s_fail != 0 || global_timer_ns() > deadline)) {
+            if (atomicExch(&s_fail, 1) == 0) fail_direct(sync, STATUS_TIMEOUT_DATA, rank, r, 0);
+            break;
+          }
+        }
+        const uint4 d = make_uint4(pa.x, pa.z, pb.x, pb.z);
+        acc = (r == 0) ? d : Vec16<T>::add(acc, d);
+      }
     }
     *reinterpret_cast<uint4*>(static_cast<char*>(out) + v * 16) = acc;
   }

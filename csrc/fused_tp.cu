@@ -251,7 +251,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmRsArgs g) {
   extern __shared__ uint8_t smem_raw[];
-  const Pipe p = carve_smem(smem_raw);
+  const Pipe p = carve_smem<3>(smem_raw);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   FusedPage* page = g.pages[g.rank];
   if (g.error_words != nullptr && *reinterpret_cast<volatile int*>(g.error_words) != 0) return;   // an earlier launch gave up
@@ -267,7 +267,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const size_t slab_bytes = static_cast<size_t>(g.rows_per_rank) * g.N * 2;
   const size_t parity_off = g.partial_off + static_cast<size_t>(parity) * g.nranks * slab_bytes;
 
-  init_pipe(p);
+  init_pipe<3>(p);
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -305,13 +305,13 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           mbar_expect_tx(&p.full_bar[stage], kStageBytes);
           tma_load_2d(a_dst, &map_a, &p.full_bar[stage], kb * BK, a_row);
           tma_load_2d(a_dst + kABytes, &map_b, &p.full_bar[stage], kb * BK, tn * BN);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (++stage == 3) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok) drain_loads(p);
+      if (!ok) drain_loads<3>(p);
     }
   } else if (warp == 1) {
-    if (lane == 0) mma_role(p, tmem_base, my_tiles, k_blocks, g.error_words);
+    if (lane == 0) mma_role<3>(p, tmem_base, my_tiles, k_blocks, g.error_words);
   } else {
     const int quarter = warp % 4;
     int acc = 0;
@@ -338,31 +338,23 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tiles_for_owner = 0;
       }
       char* slab = g.heap_bases[owner] + parity_off + static_cast<size_t>(g.rank) * slab_bytes;
-      const size_t row = static_cast<size_t>(b) * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 64) {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(taddr + c, r0);
-        tmem_ld32(taddr + c + 32, r1);
-        tc_wait_ld();
-        uint4* out = reinterpret_cast<uint4*>(slab + (row * g.N + tn * BN + c) * 2);   // 128 contiguous bytes
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-          out[v] = make_uint4(pack_bf16(__uint_as_float(r0[8 * v + 0]), __uint_as_float(r0[8 * v + 1])),
-                              pack_bf16(__uint_as_float(r0[8 * v + 2]), __uint_as_float(r0[8 * v + 3])),
-                              pack_bf16(__uint_as_float(r0[8 * v + 4]), __uint_as_float(r0[8 * v + 5])),
-                              pack_bf16(__uint_as_float(r0[8 * v + 6]), __uint_as_float(r0[8 * v + 7])));
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-          out[4 + v] = make_uint4(pack_bf16(__uint_as_float(r1[8 * v + 0]), __uint_as_float(r1[8 * v + 1])),
-                                  pack_bf16(__uint_as_float(r1[8 * v + 2]), __uint_as_float(r1[8 * v + 3])),
-                                  pack_bf16(__uint_as_float(r1[8 * v + 4]), __uint_as_float(r1[8 * v + 5])),
-                                  pack_bf16(__uint_as_float(r1[8 * v + 6]), __uint_as_float(r1[8 * v + 7])));
-      }
+      uint8_t* stage_warp = p.staging + (warp - 2) * kStagingPerWarp;
+      stage_quarter_bf16(taddr, stage_warp, lane, 1.0f);
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p.acc_empty[acc]);
+      if (lane == 0) mbar_arrive(&p.acc_empty[acc]);      // accumulator is free as soon as it sits in shared memory
+      // one row (512 contiguous bytes) per store instruction, 8 rows in flight
+      char* dst0 = slab + ((static_cast<size_t>(b) * BM + quarter * 32) * g.N + static_cast<size_t>(tn) * BN) * 2 + lane * 16;
+#pragma unroll 1
+      for (int r0 = 0; r0 < 32; r0 += 8) {
+        uint4 d[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) d[u] = *reinterpret_cast<const uint4*>(stage_warp + (r0 + u) * kStagePitch + lane * 16);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) *reinterpret_cast<uint4*>(dst0 + static_cast<size_t>(r0 + u) * g.N * 2) = d[u];
+      }
+      __syncwarp();
       ++tiles_for_owner;
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
@@ -469,9 +461,10 @@ cudaError_t launch_gemm_rs(const GemmRsArgs& g, int grid, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   CUtensorMap map_a = make_bf16_kmajor_map(g.a, static_cast<uint64_t>(g.rows_per_rank) * g.nranks, g.K, g.lda, BM);
   CUtensorMap map_b = make_bf16_kmajor_map(g.b, g.N, g.K, g.ldb, BN);
-  cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+  cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kSmemBytesStaged));
   if (e != cudaSuccess) return e;
-  gemm_rs_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(map_a, map_b, g);
+  gemm_rs_kernel<<<grid, kGemmThreads, kSmemBytesStaged, stream>>>(map_a, map_b, g);
   return cudaGetLastError();
 }
 

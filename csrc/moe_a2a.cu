@@ -304,14 +304,14 @@ finish:
 __global__ void __launch_bounds__(kGemmThreads, 1)
 moe_gemm_combine_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, MoeArgs g) {
   extern __shared__ uint8_t smem_raw[];
-  const Pipe p = carve_smem(smem_raw);
+  const Pipe p = carve_smem<3>(smem_raw);
   __shared__ MoeShared sh;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   FusedPage* page = g.pages[g.rank];
   if (g.error_words != nullptr && *reinterpret_cast<volatile int*>(g.error_words) != 0) return;
   const unsigned long long epoch = page->moe_epoch + 1;
   const int parity = static_cast<int>(epoch & 1ull);
-  init_pipe(p);
+  init_pipe<3>(p);
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -348,13 +348,13 @@ moe_gemm_combine_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
           mbar_expect_tx(&p.full_bar[stage], kStageBytes);
           tma_load_2d(a_dst, &map_a, &p.full_bar[stage], kb * BK, a_row);
           tma_load_2d(a_dst + kABytes, &map_b, &p.full_bar[stage], kb * BK, b_row);
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          if (++stage == 3) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok) drain_loads(p);
+      if (!ok) drain_loads<3>(p);
     }
   } else if (warp == 1) {
-    if (lane == 0) mma_role(p, tmem_base, my_tiles, k_blocks, g.error_words);
+    if (lane == 0) mma_role<3>(p, tmem_base, my_tiles, k_blocks, g.error_words);
   } else {
     const int quarter = warp % 4;
     int acc = 0;
@@ -375,37 +375,35 @@ moe_gemm_combine_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
       const bool valid = r_in_tile < t.rows;
       int4 m = make_int4(0, 0, 0, 0);
       if (valid) m = meta_base[static_cast<size_t>(t.expert) * g.cap + t.m0 + r_in_tile];
-      const float w = __int_as_float(m.z);
-      // the row goes home: combine[parity][copy][hidden] on the rank that owns the token
-      char* dst = g.heap_bases[valid ? m.x : g.rank] + g.moe_off + g.lay.combine_off +
-                  static_cast<size_t>(parity) * g.lay.combine_parity + static_cast<size_t>(m.y) * row_bytes +
-                  static_cast<size_t>(t.tn) * BN * 2;
+      const float w = valid ? __int_as_float(m.z) : 0.0f;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 64) {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(taddr + c, r0);
-        tmem_ld32(taddr + c + 32, r1);
-        tc_wait_ld();
-        if (valid) {
-          uint4* out = reinterpret_cast<uint4*>(dst + c * 2);
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            out[v] = make_uint4(pack_bf16(w * __uint_as_float(r0[8 * v + 0]), w * __uint_as_float(r0[8 * v + 1])),
-                                pack_bf16(w * __uint_as_float(r0[8 * v + 2]), w * __uint_as_float(r0[8 * v + 3])),
-                                pack_bf16(w * __uint_as_float(r0[8 * v + 4]), w * __uint_as_float(r0[8 * v + 5])),
-                                pack_bf16(w * __uint_as_float(r0[8 * v + 6]), w * __uint_as_float(r0[8 * v + 7])));
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            out[4 + v] = make_uint4(pack_bf16(w * __uint_as_float(r1[8 * v + 0]), w * __uint_as_float(r1[8 * v + 1])),
-                                    pack_bf16(w * __uint_as_float(r1[8 * v + 2]), w * __uint_as_float(r1[8 * v + 3])),
-                                    pack_bf16(w * __uint_as_float(r1[8 * v + 4]), w * __uint_as_float(r1[8 * v + 5])),
-                                    pack_bf16(w * __uint_as_float(r1[8 * v + 6]), w * __uint_as_float(r1[8 * v + 7])));
-        }
-      }
+      uint8_t* stage_warp = p.staging + (warp - 2) * kStagingPerWarp;
+      stage_quarter_bf16(taddr, stage_warp, lane, w);            // row = lane: scaled by its own gate weight
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p.acc_empty[acc]);
+      // every row goes home: combine[parity][copy][hidden] on the rank that owns the token.  The warp
+      // writes one row per instruction (512 contiguous bytes); the row's address comes from the lane
+      // that holds its metadata.
+      char* my_dst = nullptr;
+      if (valid)
+        my_dst = g.heap_bases[m.x] + g.moe_off + g.lay.combine_off + static_cast<size_t>(parity) * g.lay.combine_parity +
+                 static_cast<size_t>(m.y) * row_bytes + static_cast<size_t>(t.tn) * BN * 2;
+      const unsigned long long mine_u = reinterpret_cast<unsigned long long>(my_dst);
+#pragma unroll 1
+      for (int r0 = 0; r0 < 32; r0 += 8) {
+        uint4 d[8];
+        unsigned long long ptr[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          ptr[u] = __shfl_sync(0xffffffffu, mine_u, r0 + u);
+          d[u] = *reinterpret_cast<const uint4*>(stage_warp + (r0 + u) * kStagePitch + lane * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (ptr[u] != 0) *reinterpret_cast<uint4*>(reinterpret_cast<char*>(ptr[u]) + lane * 16) = d[u];
+      }
+      __syncwarp();
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
     // this warp's rows are on their way: tell every rank (one count per epilogue warp and CTA)
@@ -491,9 +489,9 @@ cudaError_t launch_moe_gemm_combine(const MoeArgs& g, int grid, cudaStream_t str
   CUtensorMap a = make_bf16_kmajor_map(g.h, static_cast<uint64_t>(g.local_experts) * g.cap, g.ffn, g.ffn, BM);
   CUtensorMap b = make_bf16_kmajor_map(g.w_down, static_cast<uint64_t>(g.local_experts) * g.hidden, g.ffn, g.ffn, BN);
   cudaError_t e = cudaFuncSetAttribute(moe_gemm_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kSmemBytes));
+                                       static_cast<int>(kSmemBytesStaged));
   if (e != cudaSuccess) return e;
-  moe_gemm_combine_kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(a, b, g);
+  moe_gemm_combine_kernel<<<grid, kGemmThreads, kSmemBytesStaged, stream>>>(a, b, g);
   return cudaGetLastError();
 }
 

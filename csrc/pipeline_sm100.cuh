@@ -35,30 +35,38 @@ __device__ __forceinline__ void red_add_release_sys(unsigned long long* p, unsig
   asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
+constexpr int kStagePitch = BN * 2 + 16;                 // bytes per staged row: 512 + 16 of padding (bank spread)
+constexpr int kStagingPerWarp = 32 * kStagePitch;        // one epilogue warp stages 32 rows x 256 bf16
+constexpr size_t kSmemBytesStaged = 1024 + 3 * static_cast<size_t>(kStageBytes) + 256 + 4 * kStagingPerWarp;
+
 struct Pipe {
+  uint8_t* staging;                                      // only valid for the 3-stage + staging layout
   uint8_t* stage_base;
   uint64_t *full_bar, *empty_bar, *acc_full, *acc_empty;
   uint32_t* tmem_slot;
   volatile int* abort_flag;
 };
 
+template <int STAGES = kStages>
 __device__ __forceinline__ Pipe carve_smem(uint8_t* smem_raw) {
   Pipe p;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   p.stage_base = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(kStages) * kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(STAGES) * kStageBytes);
   p.full_bar = bars;
-  p.empty_bar = bars + kStages;
-  p.acc_full = bars + 2 * kStages;
-  p.acc_empty = bars + 2 * kStages + 2;
-  p.tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  p.empty_bar = bars + STAGES;
+  p.acc_full = bars + 2 * STAGES;
+  p.acc_empty = bars + 2 * STAGES + 2;
+  p.tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  p.staging = smem + static_cast<size_t>(STAGES) * kStageBytes + 256;
   p.abort_flag = reinterpret_cast<volatile int*>(p.tmem_slot + 1);
   return p;
 }
 
+template <int STAGES = kStages>
 __device__ __forceinline__ void init_pipe(const Pipe& p) {
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&p.full_bar[s], 1);
       mbar_init(&p.empty_bar[s], 1);
     }
@@ -72,6 +80,7 @@ __device__ __forceinline__ void init_pipe(const Pipe& p) {
 }
 
 // MMA issuer shared by both kernels: consumes `my_tiles` tiles of k_blocks stages each.
+template <int STAGES = kStages>
 __device__ __forceinline__ void mma_role(const Pipe& p, uint32_t tmem_base, int my_tiles, int k_blocks, int* error_words) {
   constexpr uint32_t idesc = idesc_bf16_f32(BM, BN);
   int stage = 0, acc = 0;
@@ -96,18 +105,41 @@ __device__ __forceinline__ void mma_role(const Pipe& p, uint32_t tmem_base, int 
       for (int k = 0; k < BK / UMMA_K; ++k)
         umma_bf16(tmem_d, adesc + static_cast<uint64_t>(k * 2), bdesc + static_cast<uint64_t>(k * 2), idesc, (kb | k) != 0);
       tc_commit(&p.empty_bar[stage]);
-      if (++stage == kStages) { stage = 0; phase ^= 1; }
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
     tc_commit(&p.acc_full[acc]);
     if (++acc == 2) { acc = 0; acc_phase ^= 1; }
   }
 }
 
+template <int STAGES = kStages>
 __device__ __forceinline__ void drain_loads(const Pipe& p) {
-  for (int s = 0; s < kStages; ++s)
+  for (int s = 0; s < STAGES; ++s)
     for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&p.full_bar[s], 0) && !mbar_try_wait(&p.full_bar[s], 1); ++i) {}
 }
 
+
+// ---- staged epilogue -----------------------------------------------------------------------
+// An epilogue warp holds 32 rows x 256 fp32 columns of the accumulator, one row per lane.  Storing
+// from registers gives every lane its own row: fine for local HBM, wasteful over NVLink where only
+// full contiguous lines travel efficiently.  Staging the bf16 tile in shared memory lets the warp
+// write one row per instruction, 32 lanes x 16 bytes = 512 contiguous bytes.
+__device__ __forceinline__ void stage_quarter_bf16(uint32_t taddr, uint8_t* stage_warp, int lane, float scale) {
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 32) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c, r);
+    tc_wait_ld();
+    uint4* dst = reinterpret_cast<uint4*>(stage_warp + lane * kStagePitch + c * 2);
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      dst[v] = make_uint4(pack_bf16(scale * __uint_as_float(r[8 * v + 0]), scale * __uint_as_float(r[8 * v + 1])),
+                          pack_bf16(scale * __uint_as_float(r[8 * v + 2]), scale * __uint_as_float(r[8 * v + 3])),
+                          pack_bf16(scale * __uint_as_float(r[8 * v + 4]), scale * __uint_as_float(r[8 * v + 5])),
+                          pack_bf16(scale * __uint_as_float(r[8 * v + 6]), scale * __uint_as_float(r[8 * v + 7])));
+  }
+  __syncwarp();
+}
 
 }  // namespace sm100
 }  // namespace msccl

@@ -1,0 +1,53 @@
+"""Time (and give profilers a small target for) the tcgen05 GEMM on one GPU.
+
+    python -m msccl.ops.bench_gemm --m 8192 --n 3584 --k 4096 --iters 20 [--swiglu] [--cublas]
+"""
+import argparse
+import json
+
+import torch
+
+from msccl.ops.gemm import check_gemm_errors, gemm_bf16
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--m', type=int, default=8192)
+    ap.add_argument('--n', type=int, default=3584)
+    ap.add_argument('--k', type=int, default=4096)
+    ap.add_argument('--bn', type=int, default=256)
+    ap.add_argument('--iters', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--swiglu', action='store_true')
+    ap.add_argument('--cublas', action='store_true', help='also time torch.matmul (cuBLAS) on the same operands')
+    args = ap.parse_args()
+    a = torch.randn(args.m, args.k, device='cuda').bfloat16()
+    b = (torch.randn(args.n, args.k, device='cuda') * 0.02).bfloat16()
+    out = torch.empty(args.m, args.n // 2 if args.swiglu else args.n, device='cuda', dtype=torch.bfloat16)
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.iters):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / args.iters
+
+    ms = timed(lambda: gemm_bf16(a, b, out=out, bn=args.bn, epilogue='swiglu' if args.swiglu else 'none'))
+    check_gemm_errors()
+    flops = 2.0 * args.m * args.n * args.k
+    row = {'m': args.m, 'n': args.n, 'k': args.k, 'bn': args.bn, 'swiglu': args.swiglu, 'us': round(ms * 1e3, 1),
+           'tflops': round(flops / ms / 1e9, 1)}
+    if args.cublas:
+        full = torch.empty(args.m, args.n, device='cuda', dtype=torch.bfloat16)
+        ms_c = timed(lambda: torch.matmul(a, b.t(), out=full))
+        row.update({'cublas_us': round(ms_c * 1e3, 1), 'cublas_tflops': round(flops / ms_c / 1e9, 1)})
+    print(json.dumps(row))
+
+
+if __name__ == '__main__':
+    main()

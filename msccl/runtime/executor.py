@@ -181,7 +181,7 @@ class Executor:
             else:
                 algorithm = 'xml'
         if algorithm == 'oneshot':
-            ctas = max(1, min(16, nbytes // (16 * 512 * 2) or 1))
+            ctas = max(1, min(32, -(-nbytes // (16 * 512))))        # one 16-byte vector per thread
             comm.native.oneshot_allreduce(tensor.data_ptr(), tensor.data_ptr(), comm.dev_staging, nbytes,
                                           comm.ll_slot_bytes, code, comm.rank, comm.world, comm.sync_ptr(comm.rank),
                                           comm.timeout_ns, ctas, stream_h)
@@ -190,9 +190,11 @@ class Executor:
         if algorithm == 'twoshot':
             if offset is None:
                 raise PlanError('two-shot all-reduce needs a tensor from Communicator.symmetric_empty')
-            ctas = int(os.environ.get('MSCCL_TWOSHOT_CTAS', '0')) or max(1, min(128, nbytes // (128 << 10) or 1))
-            # in-switch reduction pays off from 4 ranks up; with 2 ranks plain peer loads are faster
-            use_nvls = comm.mc_base and os.environ.get('MSCCL_TWOSHOT_NVLS', '1' if comm.world > 2 else '0') == '1'
+            use_nvls = bool(comm.mc_base) and os.environ.get('MSCCL_TWOSHOT_NVLS', '1' if comm.world > 2 else '0') == '1'
+            # the switch is the bottleneck of the in-switch reduction: a few CTAs saturate it and more
+            # only add contention (measured on 8 GPUs); peer loads want many CTAs in flight
+            auto_ctas = 8 if use_nvls else max(1, min(128, nbytes // (128 << 10) or 1))
+            ctas = int(os.environ.get('MSCCL_TWOSHOT_CTAS', '0')) or auto_ctas
             comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base if use_nvls else 0, offset, nbytes, code, comm.rank,
                                           comm.world, comm.dev_syncs, comm.timeout_ns, ctas, stream_h)
             self.launches += 1
