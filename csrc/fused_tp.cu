@@ -67,13 +67,22 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
 
   if (static_cast<int>(blockIdx.x) < g.comm_ctas) {
     // ------------------------------------------------------------------ comm CTAs: push my shard
+    // Blocks are pushed in parallel, not one after the other: publishing a block costs a
+    // system-scope fence (an NVLink round trip), and doing that eight times in a row would delay
+    // the last block by tens of microseconds.  With at least as many comm CTAs as blocks, block b
+    // is handled by the CTAs c with c % blocks == b; otherwise CTA c walks blocks c, c + C, ...
     const size_t block_bytes = static_cast<size_t>(BM) * g.K * 2;
     const size_t vecs = block_bytes / 16;
-    const size_t per_cta = (vecs + g.comm_ctas - 1) / g.comm_ctas;
-    const size_t v0 = min(vecs, per_cta * blockIdx.x), v1 = min(vecs, v0 + per_cta);
+    const int C = g.comm_ctas;
+    const int parts = C >= blocks_per_rank ? C / blocks_per_rank : 1;
+    const int part = C >= blocks_per_rank ? static_cast<int>(blockIdx.x) / blocks_per_rank : 0;
+    const int b_first = C >= blocks_per_rank ? static_cast<int>(blockIdx.x) % blocks_per_rank : static_cast<int>(blockIdx.x);
+    const int b_step = C >= blocks_per_rank ? blocks_per_rank : C;
+    const size_t per_part = (vecs + parts - 1) / parts;
+    const size_t v0 = min(vecs, per_part * part), v1 = min(vecs, v0 + per_part);
     const size_t dst_off = g.gathered_off + static_cast<size_t>(parity) * g.gathered_bytes +
                            static_cast<size_t>(g.rank) * g.rows_per_rank * g.K * 2;
-    for (int b = 0; b < blocks_per_rank; ++b) {
+    for (int b = b_first; b < blocks_per_rank && part < parts; b += (C >= blocks_per_rank ? blocks_per_rank * parts : b_step)) {
       const char* src = static_cast<const char*>(g.x_local) + b * block_bytes;
       constexpr int U = 16;       // 256 bytes per thread in flight: the copy is latency bound otherwise
       for (size_t base = v0 + threadIdx.x; base < v1; base += static_cast<size_t>(blockDim.x) * U) {
@@ -104,7 +113,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
       __syncthreads();
       if (threadIdx.x == 0) {
         __threadfence_system();
-        if (atomicAdd(&page->ag_block_count[b], 1u) == static_cast<unsigned int>(g.comm_ctas) - 1u) {
+        if (atomicAdd(&page->ag_block_count[b], 1u) == static_cast<unsigned int>(parts) - 1u) {
           page->ag_block_count[b] = 0;
           __threadfence_system();
           for (int q = 1; q < g.nranks; ++q)
@@ -447,7 +456,12 @@ cudaError_t launch_ag_gemm(const AgGemmArgs& g, int epilogue, int grid, cudaStre
   CUtensorMap map_g1 = make_bf16_kmajor_map(gath + g.gathered_bytes, all_rows, g.K, g.K, BM);
   CUtensorMap map_b = make_bf16_kmajor_map(g.b, g.N, g.K, g.ldb, BN);
   auto launch = [&](auto kernel) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+    static bool configured[2] = {false, false};          // the attribute is sticky: set it once per kernel
+    cudaError_t e = cudaSuccess;
+    if (!configured[epilogue != 0]) {
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+      configured[epilogue != 0] = e == cudaSuccess;
+    }
     if (e != cudaSuccess) return e;
     kernel<<<grid, kGemmThreads, kSmemBytes, stream>>>(map_local, map_g0, map_g1, map_b, g);
     return cudaGetLastError();
@@ -461,9 +475,13 @@ cudaError_t launch_gemm_rs(const GemmRsArgs& g, int grid, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   CUtensorMap map_a = make_bf16_kmajor_map(g.a, static_cast<uint64_t>(g.rows_per_rank) * g.nranks, g.K, g.lda, BM);
   CUtensorMap map_b = make_bf16_kmajor_map(g.b, g.N, g.K, g.ldb, BN);
-  cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(kSmemBytesStaged));
-  if (e != cudaSuccess) return e;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kSmemBytesStaged));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
   gemm_rs_kernel<<<grid, kGemmThreads, kSmemBytesStaged, stream>>>(map_a, map_b, g);
   return cudaGetLastError();
 }
