@@ -22,7 +22,7 @@ namespace msccl {
 
 namespace {
 
-constexpr int kUnroll = 4;
+constexpr int kUnroll = 8;     // 16-byte vectors per thread in flight (copies are latency bound)
 
 __device__ __forceinline__ unsigned long long pack_progress(unsigned long long epoch, int iter, int step_plus_1) {
   // 32 bits of launch epoch | 20 bits of iteration | 12 bits of step+1
@@ -111,27 +111,42 @@ template <typename T, int PROTO, bool FIFO_IN, bool FIFO_OUT>
 __device__ __noinline__ void move_vectors(const char* in0, const char* in1, char* out_local, const char* fifo_in,
                                              char* fifo_out, long long fifo_base_v, long long vectors,
                                              unsigned int flag_in, unsigned int flag_out, const Waiter& w, int* fail) {
-  const long long stride = static_cast<long long>(blockDim.x) * kUnroll;
+  const long long nthreads = blockDim.x;
+  const long long stride = nthreads * kUnroll;
+  const bool reduce = in1 != nullptr;
   for (long long base = threadIdx.x; base < vectors; base += stride) {
-    uint4 val[kUnroll];
-    uint4 other[kUnroll];
+    if (base + (kUnroll - 1) * nthreads < vectors) {
+      // full group: all loads are issued before the first use, with no per-vector predicate
+      uint4 val[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      long long v = base + static_cast<long long>(u) * blockDim.x;
-      if (v < vectors) {
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long v = base + u * nthreads;
         if (FIFO_IN) {
           val[u] = Fifo<PROTO>::load(fifo_in, fifo_base_v + v, flag_in, w, fail);
         } else {
           val[u] = *reinterpret_cast<const uint4*>(in0 + v * 16);
         }
-        if (in1 != nullptr) other[u] = *reinterpret_cast<const uint4*>(in1 + v * 16);
       }
-    }
+      if (reduce) {
+        uint4 other[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      long long v = base + static_cast<long long>(u) * blockDim.x;
-      if (v < vectors) {
-        uint4 r = (in1 != nullptr) ? Vec16<T>::add(other[u], val[u]) : val[u];
+        for (int u = 0; u < kUnroll; ++u) other[u] = *reinterpret_cast<const uint4*>(in1 + (base + u * nthreads) * 16);
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) val[u] = Vec16<T>::add(other[u], val[u]);
+      }
+      if (out_local != nullptr) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) *reinterpret_cast<uint4*>(out_local + (base + u * nthreads) * 16) = val[u];
+      }
+      if (FIFO_OUT) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) Fifo<PROTO>::store(fifo_out, fifo_base_v + base + u * nthreads, val[u], flag_out);
+      }
+    } else {
+      for (long long v = base; v < vectors; v += nthreads) {
+        uint4 r = FIFO_IN ? Fifo<PROTO>::load(fifo_in, fifo_base_v + v, flag_in, w, fail)
+                          : *reinterpret_cast<const uint4*>(in0 + v * 16);
+        if (reduce) r = Vec16<T>::add(*reinterpret_cast<const uint4*>(in1 + v * 16), r);
         if (out_local != nullptr) *reinterpret_cast<uint4*>(out_local + v * 16) = r;
         if (FIFO_OUT) Fifo<PROTO>::store(fifo_out, fifo_base_v + v, r, flag_out);
       }

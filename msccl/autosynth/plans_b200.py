@@ -16,6 +16,10 @@ B200_GPU_COUNTS = (2, 4, 8)
 
 def register_b200_plans():
     manual = ThreadblockPolicy.manual
+    # One CTA moves roughly 50 GB/s, so a plan needs a few dozen CTAs per direction to fill a GPU's
+    # NVLink port; all threadblocks of a plan must also be co-resident (148 SMs).
+    copies = {2: 32, 4: 16, 8: 8}
+    small = {2: 4, 4: 2, 8: 1}     # latency-bound sizes: flag-in-data packets, few CTAs
     for n in B200_GPU_COUNTS:
         mtype = f'b200x{n}' if n != 8 else ['b200', 'b200x8']
         box = fully_connected(n)
@@ -31,23 +35,41 @@ def register_b200_plans():
             allreduce_two_shot(n)
         two_shot.__name__ = f'b200_allreduce_two_shot_{n}'
         register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='Simple',
-                               sizes=('256KB', None), instances=4, threadblock_policy=manual,
+                               sizes=('256KB', None), instances=copies[n], threadblock_policy=manual,
                                machines=lambda m: m == 1)(two_shot)
 
         def a2a(prog, nodes, n=n):
             alltoall_direct(n)
         a2a.__name__ = f'b200_alltoall_direct_{n}'
-        register_msccl_program(box, 'alltoall', mtype, chunk_factor=1, protocol='Simple', instances=4,
-                               machines=lambda m: m == 1)(a2a)
+        register_msccl_program(box, 'alltoall', mtype, chunk_factor=1, protocol='Simple', instances=copies[n],
+                               sizes=('512KB', None), machines=lambda m: m == 1)(a2a)
+
+        def a2a_ll(prog, nodes, n=n):
+            alltoall_direct(n)
+        a2a_ll.__name__ = f'b200_alltoall_direct_ll_{n}'
+        register_msccl_program(box, 'alltoall', mtype, chunk_factor=1, protocol='LL', instances=small[n],
+                               sizes=(0, '512KB'), machines=lambda m: m == 1)(a2a_ll)
 
         def ag(prog, nodes, n=n):
             allgather_direct(n)
         ag.__name__ = f'b200_allgather_direct_{n}'
-        register_msccl_program(box, 'allgather', mtype, chunk_factor=1, protocol='Simple', instances=4,
-                               machines=lambda m: m == 1)(ag)
+        register_msccl_program(box, 'allgather', mtype, chunk_factor=1, protocol='Simple', instances=copies[n],
+                               sizes=('512KB', None), machines=lambda m: m == 1)(ag)
+
+        def ag_ll(prog, nodes, n=n):
+            allgather_direct(n)
+        ag_ll.__name__ = f'b200_allgather_direct_ll_{n}'
+        register_msccl_program(box, 'allgather', mtype, chunk_factor=1, protocol='LL', instances=small[n],
+                               sizes=(0, '512KB'), machines=lambda m: m == 1)(ag_ll)
 
         def rs(prog, nodes, n=n):
             reduce_scatter_direct(n)
         rs.__name__ = f'b200_reduce_scatter_direct_{n}'
-        register_msccl_program(box, 'reduce_scatter', mtype, chunk_factor=1, protocol='Simple', instances=4,
-                               machines=lambda m: m == 1)(rs)
+        register_msccl_program(box, 'reduce_scatter', mtype, chunk_factor=1, protocol='Simple', instances=copies[n],
+                               sizes=('512KB', None), machines=lambda m: m == 1)(rs)
+
+        def rs_ll(prog, nodes, n=n):
+            reduce_scatter_direct(n)
+        rs_ll.__name__ = f'b200_reduce_scatter_direct_ll_{n}'
+        register_msccl_program(box, 'reduce_scatter', mtype, chunk_factor=1, protocol='LL', instances=small[n],
+                               sizes=(0, '512KB'), machines=lambda m: m == 1)(rs_ll)

@@ -109,7 +109,7 @@ class Communicator:
         return self
 
     @classmethod
-    def from_process_group(cls, group=None, fifo_bytes=256 << 20, arena_bytes=0, ll_max_bytes=256 << 10,
+    def from_process_group(cls, group=None, fifo_bytes=256 << 20, arena_bytes=0, ll_max_bytes=None,
                            mode=None, multicast=None):
         """One process per GPU; ``torch.distributed`` must be initialised (any backend)."""
         import torch.distributed as dist
@@ -119,6 +119,9 @@ class Communicator:
         self.world = dist.get_world_size(group)
         self.local_ranks = [self.rank]
         self.device = torch.cuda.current_device()
+        if ll_max_bytes is None:
+            # one-shot sends (n-1) copies of the message: worthwhile up to ~2 MB of total traffic
+            ll_max_bytes = max(256 << 10, (2 << 20) // self.world)
         self._set_layout(self.world, ll_max_bytes, fifo_bytes, arena_bytes)
         mode = mode or os.environ.get('MSCCL_SYMM', 'auto')
         errors = []

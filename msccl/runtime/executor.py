@@ -193,7 +193,7 @@ class Executor:
             use_nvls = bool(comm.mc_base) and os.environ.get('MSCCL_TWOSHOT_NVLS', '1' if comm.world > 2 else '0') == '1'
             # the switch is the bottleneck of the in-switch reduction: a few CTAs saturate it and more
             # only add contention (measured on 8 GPUs); peer loads want many CTAs in flight
-            auto_ctas = 8 if use_nvls else max(1, min(128, nbytes // (128 << 10) or 1))
+            auto_ctas = 8 if use_nvls else max(1, min(128, nbytes // (32 << 10) or 1))
             ctas = int(os.environ.get('MSCCL_TWOSHOT_CTAS', '0')) or auto_ctas
             comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base if use_nvls else 0, offset, nbytes, code, comm.rank,
                                           comm.world, comm.dev_syncs, comm.timeout_ns, ctas, stream_h)

@@ -139,6 +139,13 @@ def tile_geometry(plan: HostPlan, chunk_elems: int, elem_size: int, slot_bytes: 
     tile = (payload // (plan.max_cnt * elem_size)) // per_vec * per_vec
     if tile <= 0:
         raise PlanError('FIFO slot too small for this program')
+    if plan.proto == 0:
+        # Simple: a receiver starts on a tile only when the whole tile has landed, so a chunk is cut
+        # into at least four tiles (of 256 KB or more) to overlap the two sides.
+        quarter = -(-chunk_elems // 4)
+        want = max((256 << 10) // (plan.max_cnt * elem_size), quarter)
+        want = -(-want // per_vec) * per_vec
+        tile = min(tile, want)
     tile = min(tile, chunk_elems)
     iterations = -(-chunk_elems // tile)
     return tile, iterations
