@@ -10,6 +10,12 @@
 //                  multicast window); P2P mode uses plain peer loads and stores, summing in rank
 //                  order so that all ranks produce identical bits.
 //
+//   reduce-scatter: the first half of two-shot; rank r writes the sum of everyone's slice r to an
+//                  ordinary local buffer instead of publishing it.
+//   push         : all-gather and all-to-all.  Every rank stores its block(s) straight into the
+//                  destination buffers of its peers (peer stores, or one multimem.st through the
+//                  switch for all-gather), between two barriers: no staging copy on either side.
+//
 // All waits are bounded; on expiry the kernel writes a status code to the rank's sync page and
 // returns.  These are the hand-tuned counterparts of the allreduce_one_shot / allreduce_two_shot
 // MSCCLang programs (msccl/programs/allreduce.py), selected by the plan dispatcher by size.
@@ -105,7 +111,7 @@ template <> struct Multimem<__half> {
 template <typename T, bool NVLS>
 __global__ void __launch_bounds__(kDirectThreads, 1)
 twoshot_allreduce_kernel(char* const* heap_bases, char* mc, long long offset, long long bytes, int rank, int nranks,
-                         SyncPage* const* syncs, unsigned long long timeout_ns) {
+                         SyncPage* const* syncs, unsigned long long timeout_ns, char* rs_out) {
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   const unsigned long long deadline = global_timer_ns() + timeout_ns;
@@ -130,7 +136,10 @@ twoshot_allreduce_kernel(char* const* heap_bases, char* mc, long long offset, lo
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         long long i = v + static_cast<long long>(u) * blockDim.x;
-        if (i < end) Multimem<T>::st(mc + i * 16, acc[u]);
+        if (i < end) {
+          if (rs_out != nullptr) *reinterpret_cast<uint4*>(rs_out + (i - r_begin) * 16) = acc[u];
+          else Multimem<T>::st(mc + i * 16, acc[u]);
+        }
       }
     }
   } else {
@@ -156,11 +165,70 @@ twoshot_allreduce_kernel(char* const* heap_bases, char* mc, long long offset, lo
           if (r < nranks) acc = Vec16<T>::add(acc, part[u][r]);
         for (int r = R8; r < nranks; ++r)
           acc = Vec16<T>::add(acc, *reinterpret_cast<const uint4*>(heap_bases[r] + offset + i * 16));
-        for (int r = 0; r < nranks; ++r) *reinterpret_cast<uint4*>(heap_bases[(rank + r) % nranks] + offset + i * 16) = acc;
+        if (rs_out != nullptr) {
+          *reinterpret_cast<uint4*>(rs_out + (i - r_begin) * 16) = acc;
+        } else {
+          for (int r = 0; r < nranks; ++r) *reinterpret_cast<uint4*>(heap_bases[(rank + r) % nranks] + offset + i * 16) = acc;
+        }
       }
     }
   }
-  rank_barrier(syncs, rank, nranks, deadline, &s_fail);               // every slice has been published
+  rank_barrier(syncs, rank, nranks, deadline, &s_fail);               // every slice has been published (or read)
+}
+
+// ---- push: all-gather and all-to-all --------------------------------------------------------
+// Block `rank` of the destination buffer of peer p (at `dst_offset` of its heap) receives
+//   SAME_SRC (all-gather): the one source block;   otherwise (all-to-all): source block p.
+// NVLS (all-gather only): one multimem.st per vector reaches every rank through the switch.
+template <bool SAME_SRC, bool NVLS>
+__global__ void __launch_bounds__(kDirectThreads, 1)
+push_kernel(const char* src, char* const* heap_bases, char* mc, long long dst_offset, long long block_bytes, int rank,
+            int nranks, SyncPage* const* syncs, unsigned long long timeout_ns) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  const unsigned long long deadline = global_timer_ns() + timeout_ns;
+  if (!rank_barrier(syncs, rank, nranks, deadline, &s_fail)) return;   // every destination may be overwritten
+
+  constexpr int U = 8;
+  const long long vectors = block_bytes / 16;
+  const long long per_cta = (vectors + gridDim.x - 1) / gridDim.x;
+  const long long begin = min(vectors, per_cta * blockIdx.x), end = min(vectors, begin + per_cta);
+  const long long nthreads = blockDim.x;
+  const long long mine = dst_offset + block_bytes * rank;               // where my block lands in every destination
+  for (long long v = begin + threadIdx.x; v < end; v += nthreads * U) {
+    uint4 val[U];
+    if (SAME_SRC) {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (v + u * nthreads < end) val[u] = *reinterpret_cast<const uint4*>(src + (v + u * nthreads) * 16);
+      if (NVLS) {
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (v + u * nthreads < end) Multimem<float>::st(mc + mine + (v + u * nthreads) * 16, val[u]);
+      } else {
+        for (int k = 1; k <= nranks; ++k) {
+          char* dst = heap_bases[(rank + k) % nranks] + mine;
+          if (dst == src) continue;                                     // in place: my block is already there
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (v + u * nthreads < end) *reinterpret_cast<uint4*>(dst + (v + u * nthreads) * 16) = val[u];
+        }
+      }
+    } else {
+      for (int k = 1; k <= nranks; ++k) {
+        const int p = (rank + k) % nranks;
+        const char* from = src + block_bytes * p;
+        char* dst = heap_bases[p] + mine;
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (v + u * nthreads < end) val[u] = *reinterpret_cast<const uint4*>(from + (v + u * nthreads) * 16);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (v + u * nthreads < end) *reinterpret_cast<uint4*>(dst + (v + u * nthreads) * 16) = val[u];
+      }
+    }
+  }
+  rank_barrier(syncs, rank, nranks, deadline, &s_fail);                 // every block has landed
 }
 
 // ---- one-shot LL ---------------------------------------------------------------------------
@@ -258,13 +326,13 @@ oneshot_ll_allreduce_kernel(const void* in, void* out, char* const* staging, lon
 
 template <typename T>
 cudaError_t twoshot_typed(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int rank, int nranks,
-                          SyncPage* const* syncs, unsigned long long timeout_ns, int ctas, cudaStream_t stream) {
+                          SyncPage* const* syncs, unsigned long long timeout_ns, int ctas, cudaStream_t stream, char* rs_out) {
   if (mc_base != nullptr) {
     twoshot_allreduce_kernel<T, true><<<ctas, kDirectThreads, 0, stream>>>(heap_bases, mc_base + offset, offset, bytes, rank,
-                                                                         nranks, syncs, timeout_ns);
+                                                                         nranks, syncs, timeout_ns, rs_out);
   } else {
     twoshot_allreduce_kernel<T, false><<<ctas, kDirectThreads, 0, stream>>>(heap_bases, nullptr, offset, bytes, rank, nranks,
-                                                                          syncs, timeout_ns);
+                                                                          syncs, timeout_ns, rs_out);
   }
   return cudaGetLastError();
 }
@@ -281,14 +349,34 @@ cudaError_t oneshot_typed(const void* in, void* out, char* const* staging, long 
 
 cudaError_t launch_twoshot_allreduce(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int dtype,
                                      int rank, int nranks, SyncPage* const* syncs, unsigned long long timeout_ns, int ctas,
-                                     cudaStream_t stream) {
+                                     cudaStream_t stream, void* rs_out) {
   if (bytes % 16 != 0 || offset % 16 != 0 || ctas < 1 || ctas > kMaxDirectCtas || nranks > kMaxRanks) return cudaErrorInvalidValue;
+  // reduce-scatter: every rank's slice must be the same whole number of vectors
+  if (rs_out != nullptr && (bytes % (16ll * nranks) != 0 || reinterpret_cast<uintptr_t>(rs_out) % 16 != 0)) return cudaErrorInvalidValue;
+  char* out = static_cast<char*>(rs_out);
   switch (dtype) {
-    case DT_F32: return twoshot_typed<float>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream);
-    case DT_BF16: return twoshot_typed<__nv_bfloat16>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream);
-    case DT_F16: return twoshot_typed<__half>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream);
+    case DT_F32: return twoshot_typed<float>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream, out);
+    case DT_BF16: return twoshot_typed<__nv_bfloat16>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream, out);
+    case DT_F16: return twoshot_typed<__half>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream, out);
     default: return cudaErrorInvalidValue;
   }
+}
+
+cudaError_t launch_push(const void* src, bool same_src, char* const* heap_bases, char* mc_base, long long dst_offset,
+                        long long block_bytes, int rank, int nranks, SyncPage* const* syncs, unsigned long long timeout_ns,
+                        int ctas, cudaStream_t stream) {
+  if (block_bytes % 16 != 0 || dst_offset % 16 != 0 || reinterpret_cast<uintptr_t>(src) % 16 != 0 || ctas < 1 ||
+      ctas > kMaxDirectCtas || nranks > kMaxRanks)
+    return cudaErrorInvalidValue;
+  const char* s = static_cast<const char*>(src);
+  if (!same_src) {
+    push_kernel<false, false><<<ctas, kDirectThreads, 0, stream>>>(s, heap_bases, nullptr, dst_offset, block_bytes, rank, nranks, syncs, timeout_ns);
+  } else if (mc_base != nullptr) {
+    push_kernel<true, true><<<ctas, kDirectThreads, 0, stream>>>(s, heap_bases, mc_base, dst_offset, block_bytes, rank, nranks, syncs, timeout_ns);
+  } else {
+    push_kernel<true, false><<<ctas, kDirectThreads, 0, stream>>>(s, heap_bases, nullptr, dst_offset, block_bytes, rank, nranks, syncs, timeout_ns);
+  }
+  return cudaGetLastError();
 }
 
 cudaError_t launch_oneshot_allreduce(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes,

@@ -294,6 +294,9 @@ def make_run(subparsers):
         parser.add_argument('--dtype', default='bf16', choices=['bf16', 'fp16', 'fp32'])
         parser.add_argument('--iters', type=int, default=20)
         parser.add_argument('--nccl', action='store_true', help='also time torch.distributed (NCCL) on the same sizes')
+        parser.add_argument('--algo', default='auto', choices=['auto', 'direct', 'xml'],
+                            help='all-gather / reduce-scatter / all-to-all: direct kernels on symmetric memory, or '
+                                 'the registered MSCCL-IR plan through the interpreter (auto: xml if --xml is given)')
 
     def handle(args):
         if args.command not in ('run', 'bench'):

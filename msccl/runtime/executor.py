@@ -181,7 +181,8 @@ class Executor:
             else:
                 algorithm = 'xml'
         if algorithm == 'oneshot':
-            ctas = max(1, min(32, -(-nbytes // (16 * 512))))        # one 16-byte vector per thread
+            # one 16-byte vector per thread
+            ctas = int(os.environ.get('MSCCL_ONESHOT_CTAS', '0')) or max(1, min(32, -(-nbytes // (16 * 512))))
             comm.native.oneshot_allreduce(tensor.data_ptr(), tensor.data_ptr(), comm.dev_staging, nbytes,
                                           comm.ll_slot_bytes, code, comm.rank, comm.world, comm.sync_ptr(comm.rank),
                                           comm.timeout_ns, ctas, stream_h)
@@ -217,13 +218,79 @@ class Executor:
             raise PlanError(f'no {collective} plan registered for {nbytes} bytes')
         return self.run(plan, inp.view(-1), out.view(-1) if out is not None else None, stream=stream)[self.comm.rank]
 
-    def all_gather(self, output, input, stream=None):
+    def _direct_ctas(self, moved_bytes, cap=96):
+        # one sweep of a CTA is 64 KB (512 threads x 8 vectors); half of that per CTA keeps mid sizes short
+        return int(os.environ.get('MSCCL_DIRECT_CTAS', '0')) or max(1, min(cap, moved_bytes // (32 << 10)))
+
+    def all_gather(self, output, input, stream=None, algorithm='auto'):
+        """``output[r * len(input):][:len(input)] = input of rank r``.  With ``output`` from
+        ``Communicator.symmetric_empty`` every rank stores its block straight into its peers' outputs
+        (``direct``); otherwise the registered MSCCL-IR plan runs (``xml``).  ``input`` may be the
+        caller's own block of ``output`` (in place)."""
+        comm = self.comm
+        nbytes = input.numel() * input.element_size()
+        offset = None if comm.emulated_mode else comm.heap_offset_of(output)
+        if algorithm == 'auto':
+            algorithm = 'direct' if offset is not None and nbytes % 16 == 0 and input.data_ptr() % 16 == 0 else 'xml'
+        if algorithm == 'direct':
+            if offset is None:
+                raise PlanError('the direct all-gather needs an output from Communicator.symmetric_empty')
+            if output.numel() != input.numel() * comm.world:
+                raise PlanError('all-gather output must hold one input per rank')
+            use_nvls = bool(comm.mc_base) and os.environ.get('MSCCL_PUSH_NVLS', '0') == '1'
+            stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+            comm.native.push_blocks(input.data_ptr(), True, comm.dev_heap_bases, comm.mc_base if use_nvls else 0, offset, nbytes,
+                                    comm.rank, comm.world, comm.dev_syncs, comm.timeout_ns,
+                                    self._direct_ctas(nbytes * comm.world), stream_h)
+            self.launches += 1
+            return output
         return self._run_registered('allgather', input, output, stream)
 
-    def reduce_scatter(self, output, input, stream=None):
+    def reduce_scatter(self, output, input, stream=None, algorithm='auto'):
+        """``output = sum over ranks of their input[rank * len(output):][:len(output)]``.  With ``input``
+        from ``Communicator.symmetric_empty`` every rank reduces its slice straight out of its peers'
+        inputs (``direct``: peer loads in rank order, or the in-switch reduction)."""
+        comm = self.comm
+        nbytes = input.numel() * input.element_size()
+        offset = None if comm.emulated_mode else comm.heap_offset_of(input)
+        if algorithm == 'auto':
+            ok = offset is not None and nbytes % (16 * comm.world) == 0 and output.data_ptr() % 16 == 0
+            algorithm = 'direct' if ok else 'xml'
+        if algorithm == 'direct':
+            if offset is None:
+                raise PlanError('the direct reduce-scatter needs an input from Communicator.symmetric_empty')
+            if output.numel() * comm.world != input.numel() or not output.is_contiguous():
+                raise PlanError('reduce-scatter output must hold 1/world of the input')
+            use_nvls = bool(comm.mc_base) and os.environ.get('MSCCL_TWOSHOT_NVLS', '1' if comm.world > 2 else '0') == '1'
+            ctas = int(os.environ.get('MSCCL_DIRECT_CTAS', '0')) or (8 if use_nvls else self._direct_ctas(nbytes, 128))
+            stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+            comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base if use_nvls else 0, offset, nbytes,
+                                          DTYPE_CODES[input.dtype], comm.rank, comm.world, comm.dev_syncs, comm.timeout_ns,
+                                          ctas, stream_h, output.data_ptr())
+            self.launches += 1
+            return output
         return self._run_registered('reduce_scatter', input, output, stream)
 
-    def all_to_all(self, output, input, stream=None):
+    def all_to_all(self, output, input, stream=None, algorithm='auto'):
+        """``output block s = block `rank` of rank s's input`` (equal blocks).  With ``output`` from
+        ``Communicator.symmetric_empty`` every rank stores its blocks straight into its peers' outputs."""
+        comm = self.comm
+        nbytes = input.numel() * input.element_size()
+        offset = None if comm.emulated_mode else comm.heap_offset_of(output)
+        if algorithm == 'auto':
+            ok = offset is not None and nbytes % (16 * comm.world) == 0 and input.data_ptr() % 16 == 0
+            algorithm = 'direct' if ok else 'xml'
+        if algorithm == 'direct':
+            if offset is None:
+                raise PlanError('the direct all-to-all needs an output from Communicator.symmetric_empty')
+            if output.numel() != input.numel() or not input.is_contiguous():
+                raise PlanError('all-to-all input and output must have the same size')
+            stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+            comm.native.push_blocks(input.data_ptr(), False, comm.dev_heap_bases, 0, offset, nbytes // comm.world,
+                                    comm.rank, comm.world, comm.dev_syncs, comm.timeout_ns, self._direct_ctas(nbytes),
+                                    stream_h)
+            self.launches += 1
+            return output
         return self._run_registered('alltoall', input, output, stream)
 
     def check(self):

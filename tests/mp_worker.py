@@ -108,6 +108,54 @@ def main():
         comm.mc_base = saved
         dist.barrier()
 
+    # 3b. direct all-gather / all-to-all / reduce-scatter on symmetric memory (sizes with a ragged tail per CTA)
+    for blk in (2048, 1 << 16, (1 << 18) + 4096):
+        total = blk * n
+        sym_v = sym[:total]
+        mine = parts[rank][:blk].cuda()
+        for use_nvls in ([True, False] if comm.mc_base else [False]):
+            os.environ['MSCCL_PUSH_NVLS'] = '1' if use_nvls else '0'
+            sym_v.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            ex.all_gather(sym_v, mine, algorithm='direct')
+            ex.check()
+            assert torch.equal(sym_v.cpu(), torch.cat([p[:blk] for p in parts])), ('all_gather', blk, use_nvls)
+        # in place: my block is already in its slot
+        sym_v.zero_()
+        sym_v[rank * blk:(rank + 1) * blk].copy_(mine)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ex.all_gather(sym_v, sym_v[rank * blk:(rank + 1) * blk], algorithm='direct')
+        ex.check()
+        assert torch.equal(sym_v.cpu(), torch.cat([p[:blk] for p in parts])), ('all_gather in place', blk)
+        # all-to-all: block s of my output is block `rank` of rank s's input
+        src = parts[rank][:total].cuda()
+        ex.all_to_all(sym_v, src, algorithm='direct')
+        ex.check()
+        assert torch.equal(sym_v.cpu(), torch.cat([p[rank * blk:(rank + 1) * blk] for p in parts])), ('all_to_all', blk)
+        # reduce-scatter: peer loads sum in rank order (bit exact); the in-switch sum is compared in fp64
+        out = torch.empty(blk, device='cuda', dtype=torch.bfloat16)
+        for use_nvls in ([True, False] if comm.mc_base else [False]):
+            saved = comm.mc_base
+            if not use_nvls:
+                comm.mc_base = 0
+            sym_v.copy_(src)
+            torch.cuda.synchronize()
+            dist.barrier()
+            ex.reduce_scatter(out, sym_v, algorithm='direct')
+            ex.check()
+            if use_nvls:
+                ref64 = sum(p[rank * blk:(rank + 1) * blk].double() for p in parts)
+                assert torch.allclose(out.cpu().double(), ref64, rtol=2e-2, atol=2e-2), ('reduce_scatter nvls', blk)
+            else:
+                want = rank_order_sum([p[rank * blk:(rank + 1) * blk] for p in parts], torch.bfloat16)
+                assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16)), ('reduce_scatter', blk)
+            comm.mc_base = saved
+            dist.barrier()
+    if rank == 0:
+        print('direct all-gather / all-to-all / reduce-scatter: exact', flush=True)
+
     # 4. dispatcher: registered XML for a tensor outside the arena
     ex.register(program('two_shot', AllReduce(n, n, True), lambda: allreduce_two_shot(n), 2, threadblock_policy=manual))
     big = parts[rank][: n * 65536 * 4].cuda()
