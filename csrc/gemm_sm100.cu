@@ -246,6 +246,23 @@ CUtensorMap make_bf16_kmajor_map(const void* base, uint64_t rows, uint64_t cols,
   return map;
 }
 
+// Tensor map for a row-major [rows, cols] matrix of 8-bit elements (cols contiguous), box = [box_rows, 128 cols],
+// 128-byte swizzle.  `ld` is the row pitch in bytes.
+CUtensorMap make_u8_kmajor_map(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || ld % 16 != 0)
+    throw std::runtime_error("TMA needs a 16-byte aligned base address and row pitch");
+  CUtensorMap map;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+  return map;
+}
+
 int sm_count() {
   static int count = 0;
   if (count == 0) {

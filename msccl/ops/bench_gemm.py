@@ -1,6 +1,6 @@
 """Time (and give profilers a small target for) the tcgen05 GEMM on one GPU.
 
-    python -m msccl.ops.bench_gemm --m 8192 --n 3584 --k 4096 --iters 20 [--swiglu] [--cublas]
+    python -m msccl.ops.bench_gemm --m 8192 --n 3584 --k 4096 --iters 20 [--swiglu] [--fp8] [--cublas]
 """
 import argparse
 import json
@@ -19,6 +19,7 @@ def main():
     ap.add_argument('--iters', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--swiglu', action='store_true')
+    ap.add_argument('--fp8', action='store_true', help='block-scaled e4m3 kernel (MX scales per 32 K elements)')
     ap.add_argument('--cublas', action='store_true', help='also time torch.matmul (cuBLAS) on the same operands')
     args = ap.parse_args()
     a = torch.randn(args.m, args.k, device='cuda').bfloat16()
@@ -37,10 +38,17 @@ def main():
         torch.cuda.synchronize()
         return start.elapsed_time(stop) / args.iters
 
-    ms = timed(lambda: gemm_bf16(a, b, out=out, bn=args.bn, epilogue='swiglu' if args.swiglu else 'none'))
+    if args.fp8:
+        from msccl.ops.gemm import gemm_mxfp8, pack_mx_scales, quantize_mxfp8
+        aq, sa = quantize_mxfp8(a.float())
+        bq, sb = quantize_mxfp8(b.float())
+        sa, sb = pack_mx_scales(sa), pack_mx_scales(sb)
+        ms = timed(lambda: gemm_mxfp8(aq, sa, bq, sb, out=out))
+    else:
+        ms = timed(lambda: gemm_bf16(a, b, out=out, bn=args.bn, epilogue='swiglu' if args.swiglu else 'none'))
     check_gemm_errors()
     flops = 2.0 * args.m * args.n * args.k
-    row = {'m': args.m, 'n': args.n, 'k': args.k, 'bn': args.bn, 'swiglu': args.swiglu, 'us': round(ms * 1e3, 1),
+    row = {'m': args.m, 'n': args.n, 'k': args.k, 'bn': 128 if args.fp8 else args.bn, 'swiglu': args.swiglu, 'fp8': args.fp8, 'us': round(ms * 1e3, 1),
            'tflops': round(flops / ms / 1e9, 1)}
     if args.cublas:
         full = torch.empty(args.m, args.n, device='cuda', dtype=torch.bfloat16)

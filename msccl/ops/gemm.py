@@ -63,3 +63,66 @@ def gemm_bf16(a, b, out=None, epilogue='none', bn=256, max_ctas=0, stream=None):
     load().gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
                      1 if swiglu else 0, bn, _errors(a.device).data_ptr(), max_ctas, stream_h)
     return out
+
+
+# ---------------------------------------------------------------------------- block-scaled fp8
+MX_BLOCK = 32          # K elements that share one scale
+_E4M3_MAX = 448.0
+
+
+def quantize_mxfp8(x):
+    """Quantise ``x`` [R, K] (K % 32 == 0) to the MX fp8 format: e4m3 values plus one UE8M0 scale byte
+    (``2 ** (byte - 127)``) per 32 consecutive K elements of a row, chosen as the smallest power of two
+    that brings the block's largest magnitude inside the e4m3 range.  Returns ``(q, scales)`` with
+    ``q`` [R, K] float8_e4m3fn and ``scales`` [R, K / 32] uint8."""
+    r, k = x.shape
+    assert k % MX_BLOCK == 0
+    blocks = x.float().reshape(r, k // MX_BLOCK, MX_BLOCK)
+    amax = blocks.abs().amax(dim=-1).clamp_min(2.0 ** -120)
+    exp = torch.ceil(torch.log2(amax / _E4M3_MAX)).clamp(-127, 127)
+    q = (blocks / torch.exp2(exp).unsqueeze(-1)).clamp(-_E4M3_MAX, _E4M3_MAX).reshape(r, k).to(torch.float8_e4m3fn)
+    return q, (exp + 127).to(torch.uint8)
+
+
+def dequantize_mxfp8(q, scales):
+    """fp32 values of a ``quantize_mxfp8`` pair."""
+    r, k = q.shape
+    s = torch.exp2(scales.float() - 127.0).repeat_interleave(MX_BLOCK, dim=1)
+    return q.float() * s
+
+
+def pack_mx_scales(scales):
+    """Arrange ``scales`` [R, K / 32] (K % 128 == 0) the way the kernel's tensor-memory copy consumes them:
+    one 512-byte block per (128 rows, 128 K elements), byte ``(r % 32) * 16 + (r // 32) * 4 + j`` of a block
+    = scale of row ``r`` for K elements ``[32 j, 32 j + 32)``.  Rows are padded to a multiple of 128 with
+    the scale 1.0.  Returns a flat uint8 tensor."""
+    r, kb4 = scales.shape
+    assert kb4 % 4 == 0 and scales.dtype == torch.uint8
+    tiles = -(-r // 128)
+    padded = torch.full((tiles * 128, kb4), 127, dtype=torch.uint8, device=scales.device)
+    padded[:r] = scales
+    v = padded.view(tiles, 4, 32, kb4 // 4, 4)            # [tile, r // 32, r % 32, k block, j]
+    return v.permute(0, 3, 2, 1, 4).contiguous().view(-1)
+
+
+def gemm_mxfp8(a, sfa_packed, b, sfb_packed, out=None, max_ctas=0, stream=None):
+    """``a``: [M, K] e4m3, ``b``: [N, K] e4m3, scales packed by ``pack_mx_scales``.  Returns bf16 [M, N] =
+    dequant(a) @ dequant(b).T with the scaling done inside the tensor core (tcgen05 block_scale MMA)."""
+    assert a.is_cuda and b.is_cuda and a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    m, k = a.shape
+    n, kb = b.shape
+    assert k == kb, 'inner dimensions differ'
+    if k % 128 or n % 128:
+        raise ValueError(f'K and N must be multiples of 128 (got K={k}, N={n})')
+    need_a, need_b = -(-m // 128) * (k // 128) * 512, (n // 128) * (k // 128) * 512
+    if sfa_packed.numel() != need_a or sfb_packed.numel() != need_b:
+        raise ValueError(f'packed scales must hold {need_a} and {need_b} bytes')
+    assert sfa_packed.dtype == torch.uint8 and sfb_packed.dtype == torch.uint8 and sfa_packed.is_contiguous()
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    assert out.shape == (m, n) and out.stride(1) == 1 and out.dtype == torch.bfloat16
+    stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+    load().gemm_mxfp8(a.data_ptr(), sfa_packed.data_ptr(), b.data_ptr(), sfb_packed.data_ptr(), out.data_ptr(), m, n, k,
+                      a.stride(0), b.stride(0), out.stride(0), _errors(a.device).data_ptr(), max_ctas, stream_h)
+    return out

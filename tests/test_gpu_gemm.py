@@ -61,3 +61,31 @@ def test_gemm_strided_operands_and_few_ctas():
     want = _ref(a, b)
     assert (out[:, 256:768].float() - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-3
     assert torch.all(out[:, :256] == 0) and torch.all(out[:, 768:] == 0)
+
+
+@pytest.mark.parametrize('m,n,k', [(128, 128, 128), (256, 256, 512), (300, 384, 1024), (1024, 2048, 2048)])
+def test_gemm_mxfp8_block_scaled(m, n, k):
+    # block-scaled fp8 (one power-of-two scale per 32 K elements of a row, applied by the tensor core)
+    # against the fp32 product of the dequantised operands; rows and K blocks get widely different
+    # magnitudes so that a scale landing on the wrong row or block is far outside the tolerance
+    from msccl.ops import check_gemm_errors
+    from msccl.ops.gemm import dequantize_mxfp8, gemm_mxfp8, pack_mx_scales, quantize_mxfp8
+    gen = torch.Generator(device='cuda').manual_seed(m + n + k)
+
+    def operand(rows):
+        x = torch.randn(rows, k, device='cuda', generator=gen)
+        row_mag = torch.exp2(torch.randint(-4, 5, (rows, 1), device='cuda', generator=gen).float())
+        blk_mag = torch.exp2(torch.randint(-3, 4, (rows, k // 32), device='cuda', generator=gen).float())
+        return x * row_mag * blk_mag.repeat_interleave(32, dim=1)
+
+    aq, sa = quantize_mxfp8(operand(m))
+    bq, sb = quantize_mxfp8(operand(n))
+    d = gemm_mxfp8(aq, pack_mx_scales(sa), bq, pack_mx_scales(sb))
+    check_gemm_errors()
+    want = dequantize_mxfp8(aq, sa) @ dequantize_mxfp8(bq, sb).t()
+    err = (d.float() - want).abs().max().item()
+    scale = want.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-3, (err, scale)
+    # row-wise check as well: a small row must not hide behind a large one
+    row_scale = want.abs().amax(dim=1)
+    assert torch.all((d.float() - want).abs().amax(dim=1) <= 2e-2 * row_scale + 1e-3)
