@@ -222,6 +222,15 @@ PYBIND11_MODULE(_msccl_native, m) {
                                      reinterpret_cast<int*>(error_words), max_ctas, as_stream(stream)),
              "launch of the tcgen05 GEMM kernel");
   });
+  // The same product on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles).
+  m.def("gemm_bf16_2cta", [](uintptr_t a, uintptr_t b, uintptr_t d, int M, int N, int K, int lda, int ldb, int ldd, int epilogue,
+                              uintptr_t error_words, int max_pairs, uintptr_t stream) {
+    check_rt(msccl::sm100::gemm_bf16_2cta(reinterpret_cast<const void*>(a), reinterpret_cast<const void*>(b),
+                                          reinterpret_cast<void*>(d), M, N, K, lda, ldb, ldd, epilogue,
+                                          reinterpret_cast<int*>(error_words), max_pairs, as_stream(stream)),
+             "launch of the two-CTA tcgen05 GEMM kernel");
+  });
+  m.def("max_cta_pairs", [](int epilogue) { return msccl::sm100::max_cta_pairs(epilogue); });
   // D (bf16) = block-scaled e4m3 A[M,K] * B[N,K]^T; sfa / sfb: UE8M0 scales in 512-byte blocks per (128 rows, 128 K).
   m.def("gemm_mxfp8", [](uintptr_t a, uintptr_t sfa, uintptr_t b, uintptr_t sfb, uintptr_t d, int M, int N, int K, int lda,
                           int ldb, int ldd, uintptr_t error_words, int max_ctas, uintptr_t stream) {

@@ -33,6 +33,7 @@ namespace {
 constexpr int FBN = 128;                       // tile columns
 constexpr int FBK = 128;                       // K elements (= bytes) per stage
 constexpr int kF8Stages = 6;
+constexpr int kF8GroupM = 16;                  // tile rows per L2-resident group
 constexpr int kF8ABytes = BM * FBK;            // 16 KB
 constexpr int kF8BBytes = FBN * FBK;           // 16 KB
 constexpr int kSfBytes = 512;                  // scales of 128 rows x 128 K
@@ -124,7 +125,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, kF8GroupM, tm, tn);
         const uint8_t* sfa_tile = sfa + static_cast<size_t>(tm) * k_blocks * kSfBytes;
         const uint8_t* sfb_tile = sfb + static_cast<size_t>(tn) * k_blocks * kSfBytes;
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -201,7 +203,8 @@ gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, kF8GroupM, tm, tn);
       bool ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {

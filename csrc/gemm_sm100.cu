@@ -16,6 +16,8 @@ namespace sm100 {
 
 namespace {
 
+constexpr int kGroupM = 16;          // 16 tile rows = 2048 rows of A per L2-resident group
+
 template <int BN> struct GemmSmem {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kABytes = BM * BK * 2;
@@ -78,7 +80,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       int issued_unconsumed = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, kGroupM, tm, tn);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             gemm_fail(error_words, abort_flag, GEMM_TIMEOUT_EMPTY, 0, stage);
@@ -146,7 +149,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, kGroupM, tm, tn);
       bool ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {

@@ -134,6 +134,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Tile order of the persistent kernels.  Tiles that run at the same time have consecutive indices;
+// walking `group_m` tile rows per tile column before moving to the next column keeps the A rows of a
+// group (group_m x tile_rows x K) and the B columns in flight resident in L2.  Plain column-major
+// order re-reads all of A from HBM once per tile column as soon as A outgrows L2.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int per_group = group_m * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * group_m;
+  const int rows = min(group_m, tiles_m - first_m);
+  const int in_group = tile - g * per_group;
+  tm = first_m + in_group % rows;
+  tn = in_group / rows;
+}
+
 // Error word layout in global memory: [0] code (0 ok), [1] block, [2] role, [3] detail.
 enum GemmError : int { GEMM_OK = 0, GEMM_TIMEOUT_FULL = 1, GEMM_TIMEOUT_EMPTY = 2, GEMM_TIMEOUT_ACC = 3, GEMM_TIMEOUT_FLAG = 4 };
 

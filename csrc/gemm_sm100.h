@@ -15,6 +15,10 @@ int sm_count();
 cudaError_t gemm_bf16(const void* a, const void* b, void* d, int M, int N, int K, int lda, int ldb, int ldd, int epilogue,
                       int bn, int* error_words, int max_ctas, cudaStream_t stream);
 
+// Two-CTA (cta_group::2) variant with 256 x 256 tiles per CTA pair, see gemm_2cta_sm100.cu.  N % 256 == 0.
+cudaError_t gemm_bf16_2cta(const void* a, const void* b, void* d, int M, int N, int K, int lda, int ldb, int ldd, int epilogue,
+                           int* error_words, int max_pairs, cudaStream_t stream);
+int max_cta_pairs(int epilogue);
 // Block-scaled fp8 (e4m3 with one UE8M0 scale per 32 K elements), see gemm_mxfp8_sm100.cu.
 cudaError_t gemm_mxfp8(const void* a, const void* sfa, const void* b, const void* sfb, void* d, int M, int N, int K, int lda,
                        int ldb, int ldd, int* error_words, int max_ctas, cudaStream_t stream);

@@ -19,6 +19,7 @@ def main():
     ap.add_argument('--iters', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--swiglu', action='store_true')
+    ap.add_argument('--pair', type=int, default=-1, help='1: CTA-pair kernel (cta_group::2), 0: single-CTA kernel, -1: default')
     ap.add_argument('--fp8', action='store_true', help='block-scaled e4m3 kernel (MX scales per 32 K elements)')
     ap.add_argument('--cublas', action='store_true', help='also time torch.matmul (cuBLAS) on the same operands')
     args = ap.parse_args()
@@ -45,10 +46,11 @@ def main():
         sa, sb = pack_mx_scales(sa), pack_mx_scales(sb)
         ms = timed(lambda: gemm_mxfp8(aq, sa, bq, sb, out=out))
     else:
-        ms = timed(lambda: gemm_bf16(a, b, out=out, bn=args.bn, epilogue='swiglu' if args.swiglu else 'none'))
+        ms = timed(lambda: gemm_bf16(a, b, out=out, bn=args.bn, epilogue='swiglu' if args.swiglu else 'none',
+                                     pair=None if args.pair < 0 else bool(args.pair)))
     check_gemm_errors()
     flops = 2.0 * args.m * args.n * args.k
-    row = {'m': args.m, 'n': args.n, 'k': args.k, 'bn': 128 if args.fp8 else args.bn, 'swiglu': args.swiglu, 'fp8': args.fp8, 'us': round(ms * 1e3, 1),
+    row = {'m': args.m, 'n': args.n, 'k': args.k, 'bn': 128 if args.fp8 else args.bn, 'swiglu': args.swiglu, 'fp8': args.fp8, 'pair': args.pair, 'us': round(ms * 1e3, 1),
            'tflops': round(flops / ms / 1e9, 1)}
     if args.cublas:
         full = torch.empty(args.m, args.n, device='cuda', dtype=torch.bfloat16)

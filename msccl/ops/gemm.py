@@ -3,6 +3,8 @@
 memory, bf16 result.  ``epilogue='swiglu'`` fuses ``silu(gate) * up`` where each 256-column tile
 of B holds 128 gate rows followed by the 128 matching up rows (see ``interleave_gate_up``).
 """
+import os
+
 import torch
 
 from msccl.runtime.native import load
@@ -45,8 +47,10 @@ def interleave_gate_up(w_gate, w_up, tile=256):
     return torch.cat([g, u], dim=1).reshape(2 * f, k).contiguous()
 
 
-def gemm_bf16(a, b, out=None, epilogue='none', bn=256, max_ctas=0, stream=None):
-    """``a``: [M, K] bf16, ``b``: [N, K] bf16 (row pitch may exceed K).  Returns [M, N] (or [M, N/2] for swiglu)."""
+def gemm_bf16(a, b, out=None, epilogue='none', bn=256, max_ctas=0, stream=None, pair=None):
+    """``a``: [M, K] bf16, ``b``: [N, K] bf16 (row pitch may exceed K).  Returns [M, N] (or [M, N/2] for swiglu).
+    ``pair``: run on CTA pairs (``tcgen05 cta_group::2``, 256 x 256 tiles; needs N % 256 == 0); ``None`` takes
+    ``MSCCL_GEMM_PAIR`` (default on) whenever the shape allows it and ``bn`` is 256."""
     assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     m, k = a.shape
@@ -60,6 +64,14 @@ def gemm_bf16(a, b, out=None, epilogue='none', bn=256, max_ctas=0, stream=None):
         out = torch.empty(m, n_out, dtype=torch.bfloat16, device=a.device)
     assert out.shape == (m, n_out) and out.stride(1) == 1 and out.dtype == torch.bfloat16
     stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+    if pair is None:
+        pair = bn == 256 and n % 256 == 0 and os.environ.get('MSCCL_GEMM_PAIR', '1') == '1'
+    if pair:
+        if n % 256:
+            raise ValueError(f'the two-CTA kernel needs N to be a multiple of 256 (got {n})')
+        load().gemm_bf16_2cta(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
+                              1 if swiglu else 0, _errors(a.device).data_ptr(), (max_ctas + 1) // 2, stream_h)
+        return out
     load().gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), b.stride(0), out.stride(0),
                      1 if swiglu else 0, bn, _errors(a.device).data_ptr(), max_ctas, stream_h)
     return out

@@ -89,3 +89,34 @@ def test_gemm_mxfp8_block_scaled(m, n, k):
     # row-wise check as well: a small row must not hide behind a large one
     row_scale = want.abs().amax(dim=1)
     assert torch.all((d.float() - want).abs().amax(dim=1) <= 2e-2 * row_scale + 1e-3)
+
+
+@pytest.mark.parametrize('m,n,k', [(256, 256, 64), (256, 512, 512), (1000, 768, 1024), (4096, 4096, 2048)])
+def test_gemm_cta_pair_matches_reference(m, n, k):
+    # tcgen05 cta_group::2: two CTAs share one 256 x 256 tile
+    from msccl.ops import check_gemm_errors, gemm_bf16
+    gen = torch.Generator(device='cuda').manual_seed(m * 7 + n + k)
+    a = torch.randn(m, k, device='cuda', generator=gen).bfloat16()
+    b = (torch.randn(n, k, device='cuda', generator=gen) * 0.05).bfloat16()
+    d = gemm_bf16(a, b, pair=True)
+    check_gemm_errors()
+    want = _ref(a, b)
+    assert (d.float() - want).abs().max().item() <= 1e-2 * want.abs().max().item() + 1e-3
+    # the single-CTA kernel accumulates in the same order: identical bits
+    assert torch.equal(d, gemm_bf16(a, b, pair=False))
+
+
+def test_gemm_cta_pair_identity_and_swiglu():
+    from msccl.ops import check_gemm_errors, gemm_bf16
+    from msccl.ops.gemm import interleave_gate_up
+    a = torch.randn(512, 256, device='cuda').bfloat16()
+    eye = torch.eye(256, device='cuda').bfloat16()
+    assert torch.equal(gemm_bf16(a, eye, pair=True), a)
+    gen = torch.Generator(device='cuda').manual_seed(5)
+    x = torch.randn(384, 512, device='cuda', generator=gen).bfloat16()
+    wg = (torch.randn(768, 512, device='cuda', generator=gen) * 0.05).bfloat16()
+    wu = (torch.randn(768, 512, device='cuda', generator=gen) * 0.05).bfloat16()
+    w = interleave_gate_up(wg, wu)
+    h = gemm_bf16(x, w, epilogue='swiglu', pair=True)
+    check_gemm_errors()
+    assert torch.equal(h, gemm_bf16(x, w, epilogue='swiglu', pair=False))
