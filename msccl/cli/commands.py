@@ -219,6 +219,8 @@ def make_handle_ncclize(subparsers):
                         default=ChannelPolicy.MatchTopology, help='channel allocation policy')
     parser.add_argument('--instances', type=int, default=1,
                         help='number of interleaved instances of the algorithm to make')
+    parser.add_argument('--copy-threadblocks', type=int, default=1,
+                        help='threadblocks that share the local copies of a rank (1 = reference layout)')
 
     def handle(args):
         if args.command != 'ncclize':
@@ -230,6 +232,7 @@ def make_handle_ncclize(subparsers):
                            pretty_print=not args.no_pretty_print, use_scratch=not args.no_scratch,
                            merge_contiguous=not args.no_merge_contiguous,
                            greedy_scratch_sorting=args.greedy_scratch_sorting, instances=args.instances,
+                           copy_threadblocks=args.copy_threadblocks,
                            logging=True)
             sink.write(args, lambda: text, name_msccl_object(algo.name, ending='msccl.xml'))
         return True
@@ -294,6 +297,8 @@ def make_run(subparsers):
         parser.add_argument('--dtype', default='bf16', choices=['bf16', 'fp16', 'fp32'])
         parser.add_argument('--iters', type=int, default=20)
         parser.add_argument('--nccl', action='store_true', help='also time torch.distributed (NCCL) on the same sizes')
+        parser.add_argument('--suite', action='store_true',
+                            help='all four collectives, direct kernels and registered plans, each verified against NCCL')
         parser.add_argument('--algo', default='auto', choices=['auto', 'direct', 'xml'],
                             help='all-gather / reduce-scatter / all-to-all: direct kernels on symmetric memory, or '
                                  'the registered MSCCL-IR plan through the interpreter (auto: xml if --xml is given)')

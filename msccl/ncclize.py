@@ -313,8 +313,14 @@ def _spread_over_channels(intervals, num_chans):
 
 def ncclize(algorithm, remap_scratch=None, channel_policy=ChannelPolicy.MatchTopology, pretty_print=True,
             use_scratch=True, merge_contiguous=True, greedy_scratch_sorting=False, instances=1,
-            logging=False):
-    """Return the MSCCL-IR XML text (proto ``Simple``, ``inplace="0"``) for ``algorithm``."""
+            logging=False, copy_threadblocks=1):
+    """Return the MSCCL-IR XML text (proto ``Simple``, ``inplace="0"``) for ``algorithm``.
+
+    ``copy_threadblocks``: the local copies of a rank (input to scratch before, input or scratch to output
+    after) run on this many threadblocks, each taking an equal share of every copy's chunks.  1 is the
+    reference layout (one copy threadblock per rank, reference ncclize.py:622-630); on an executor that
+    gives every threadblock its own SM a single block copying a large buffer becomes the critical path,
+    and ``copy_threadblocks=instances`` removes it."""
     if algorithm.is_pipelined():
         raise ValueError('Pipelining is not supported.')
     if remap_scratch is None:
@@ -359,6 +365,17 @@ def ncclize(algorithm, remap_scratch=None, channel_policy=ChannelPolicy.MatchTop
                 cp.src_offset *= instances
                 cp.dst_offset *= instances
                 cp.cnt *= instances
+        if copy_threadblocks > 1:
+            for copies in (g.precopies, g.postcopies):
+                pieces = []
+                for cp in copies:
+                    share = -(-cp.cnt // copy_threadblocks)
+                    for slot, first in enumerate(range(0, cp.cnt, share)):
+                        piece = _Op(cp.gpu, None, cp.step, False, 'cpy', cp.src_buffer, cp.src_offset + first,
+                                    cp.dst_buffer, cp.dst_offset + first, min(share, cp.cnt - first), [])
+                        piece.copy_slot = slot
+                        pieces.append(piece)
+                copies[:] = pieces
 
     # 3-5. ops with dependencies
     by_channel = defaultdict(list)
@@ -498,9 +515,11 @@ def ncclize(algorithm, remap_scratch=None, channel_policy=ChannelPolicy.MatchTop
     for rank, g in gpus.items():
         g.threadblocks = sorted((tb for tbs in pools[rank].values() for tb in tbs),
                                 key=lambda tb: (tb.send, tb.recv, tb.channel))
-        copies = _Threadblock(0)
-        copies.steps = g.precopies + g.postcopies
-        g.threadblocks.append(copies)
+        slots = sorted({getattr(cp, 'copy_slot', 0) for cp in g.precopies + g.postcopies} | {0})
+        for slot in slots:
+            copies = _Threadblock(0)
+            copies.steps = [cp for cp in g.precopies + g.postcopies if getattr(cp, 'copy_slot', 0) == slot]
+            g.threadblocks.append(copies)
         for i, tb in enumerate(g.threadblocks):
             tb.rbid = i
             for op in tb.steps:

@@ -37,7 +37,7 @@ def _timed(fn, iters, dist):
     return float(t.item())
 
 
-def main_from_args(args, check=False):
+def _setup(args, collectives, hi):
     import torch.distributed as dist
     import msccl
     from msccl.runtime import Communicator, Executor
@@ -49,9 +49,6 @@ def main_from_args(args, check=False):
     torch.cuda.set_device(local)
     dist.init_process_group('nccl', device_id=torch.device('cuda', local))
     rank, n = dist.get_rank(), dist.get_world_size()
-    dtype = _DTYPES[args.dtype]
-    esize = torch.empty((), dtype=dtype).element_size()
-    lo, hi = parse_size(args.min_bytes), parse_size(args.max_bytes)
     comm = Communicator.from_process_group(arena_bytes=hi + (8 << 20))
     ex = Executor(comm)
     if args.xml is not None:
@@ -59,90 +56,137 @@ def main_from_args(args, check=False):
     else:
         machine = 'b200' if n == 8 else f'b200x{n}'
         if rank == 0:
-            msccl.init(machine, 1, (args.collective, (0, None)))
+            msccl.init(machine, 1, *[(c, (0, None)) for c in collectives])
             path = [os.environ.get('MSCCL_CONFIG')]
         else:
             path = [None]
         dist.broadcast_object_list(path, src=0)
         if path[0]:
             ex.load_plan_table(path[0])
-    coll = args.collective
+    return dist, comm, ex, rank, n
+
+
+def _one_size(dist, comm, ex, rank, n, coll, mode, size, dtype, check, nccl):
+    """One row (dict) for ``coll`` at ``size`` bytes, or None if nothing can run it."""
+    esize = torch.empty((), dtype=dtype).element_size()
+    numel = size // esize // (n * 16) * (n * 16)
+    if numel == 0:
+        return None
+    nbytes = numel * esize
+    gen = torch.Generator(device='cuda').manual_seed(1 + rank)
+    plan = None
+    if coll == 'allreduce':
+        sym = comm.tensor_at(comm.rank, comm.off_arena, numel, dtype)
+        src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
+        if mode == 'xml':
+            work = src.clone()
+            fn = lambda: ex.all_reduce(work, algorithm='xml')                          # noqa: E731
+            if ex.select('allreduce', nbytes) is None:
+                return None
+        else:
+            fn = lambda: ex.all_reduce(sym)                                            # noqa: E731
+        ref_fn = lambda t: dist.all_reduce(t)                                          # noqa: E731
+        algo = 'auto' if mode != 'xml' else ex.select('allreduce', nbytes).algo.name
+    else:
+        if mode == 'xml':
+            plan = ex.select(coll, nbytes if coll != 'allgather' else nbytes // n)
+            if plan is None:
+                return None
+        algo = plan.algo.name if plan is not None else 'direct'
+        sym = comm.tensor_at(comm.rank, comm.off_arena, numel, dtype)       # symmetric side of the direct kernels
+        if coll == 'allgather':
+            src = torch.randn(numel // n, device='cuda', generator=gen).to(dtype)
+            out = torch.empty(numel, device='cuda', dtype=dtype)
+            ref_fn = lambda t: dist.all_gather_into_tensor(out, t)                    # noqa: E731
+            direct = lambda: ex.all_gather(sym, src, algorithm='direct')              # noqa: E731
+        elif coll == 'reduce_scatter':
+            src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
+            out = torch.empty(numel // n, device='cuda', dtype=dtype)
+            ref_fn = lambda t: dist.reduce_scatter_tensor(out, t)                     # noqa: E731
+            sym.copy_(src)
+            direct = lambda: ex.reduce_scatter(mine, sym, algorithm='direct')         # noqa: E731
+        else:
+            src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
+            out = torch.empty(numel, device='cuda', dtype=dtype)
+            ref_fn = lambda t: dist.all_to_all_single(out, t)                         # noqa: E731
+            direct = lambda: ex.all_to_all(sym, src, algorithm='direct')              # noqa: E731
+        mine = torch.empty_like(out)
+        if plan is not None:
+            fn = lambda: ex.run(plan, src, mine)                                       # noqa: E731
+        else:
+            fn = direct
+    row = {'collective': coll, 'algo': algo, 'nranks': n, 'bytes': nbytes}
+    if check:
+        if coll == 'allreduce':
+            if mode == 'xml':
+                work.copy_(src)
+                got = work
+            else:
+                sym.copy_(src)
+                got = sym
+            fn()
+            want = src.clone()
+            ref_fn(want)
+        else:
+            fn()
+            ref_fn(src)
+            got, want = (mine if plan is not None or coll == 'reduce_scatter' else sym), out
+        ex.check()
+        row['matches_nccl'] = bool(torch.allclose(got.float(), want.float(), rtol=3e-2, atol=3e-2))
+        if not row['matches_nccl'] or not nccl:
+            return row
+    iters = 50 if nbytes <= (1 << 22) else 10
+    ms = _timed(fn, iters, dist)
+    ex.check()
+    row.update({'time_us': round(ms * 1e3, 2), 'algbw_gbs': round(nbytes / ms / 1e6, 2),
+                'busbw_gbs': round(nbytes * _bus_factor(coll, n) / ms / 1e6, 2)})
+    if nccl:
+        t = src.clone()
+        nccl_ms = _timed(lambda: ref_fn(t), iters, dist)
+        row['nccl_time_us'] = round(nccl_ms * 1e3, 2)
+        row['nccl_busbw_gbs'] = round(nbytes * _bus_factor(coll, n) / nccl_ms / 1e6, 2)
+    return row
+
+
+def _sizes(lo, hi):
     size = lo
     while size <= hi:
-        numel = size // esize // (n * 16) * (n * 16)
-        if numel == 0:
-            size *= 4
-            continue
-        nbytes = numel * esize
-        gen = torch.Generator(device='cuda').manual_seed(1 + rank)
-        if coll == 'allreduce':
-            sym, _ = (comm.tensor_at(comm.rank, comm.off_arena, numel, dtype), 0)
-            src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
-            fn = lambda: ex.all_reduce(sym)                                               # noqa: E731
-            ref_fn = lambda t: dist.all_reduce(t)                                          # noqa: E731
-            algo = 'auto'
-        else:
-            mode = getattr(args, 'algo', 'auto')
-            if mode == 'auto':
-                mode = 'xml' if args.xml is not None else 'direct'
-            plan = None
-            if mode == 'xml':
-                plan = ex.select(coll, nbytes if coll != 'allgather' else nbytes // n)
-                if plan is None:
-                    size *= 4
-                    continue
-            algo = plan.algo.name if plan is not None else 'direct'
-            sym = comm.tensor_at(comm.rank, comm.off_arena, numel, dtype)       # symmetric side of the direct kernels
-            if coll == 'allgather':
-                src = torch.randn(numel // n, device='cuda', generator=gen).to(dtype)
-                out = torch.empty(numel, device='cuda', dtype=dtype)
-                ref_fn = lambda t: dist.all_gather_into_tensor(out, t)                    # noqa: E731
-                direct = lambda: ex.all_gather(sym, src, algorithm='direct')              # noqa: E731
-            elif coll == 'reduce_scatter':
-                src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
-                out = torch.empty(numel // n, device='cuda', dtype=dtype)
-                ref_fn = lambda t: dist.reduce_scatter_tensor(out, t)                     # noqa: E731
-                sym.copy_(src)
-                direct = lambda: ex.reduce_scatter(mine, sym, algorithm='direct')         # noqa: E731
-            else:
-                src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
-                out = torch.empty(numel, device='cuda', dtype=dtype)
-                ref_fn = lambda t: dist.all_to_all_single(out, t)                         # noqa: E731
-                direct = lambda: ex.all_to_all(sym, src, algorithm='direct')              # noqa: E731
-            mine = torch.empty_like(out)
-            if plan is not None:
-                fn = lambda: ex.run(plan, src, mine)                                       # noqa: E731
-            else:
-                fn = direct
-        if check:
-            if coll == 'allreduce':
-                sym.copy_(src)
-                fn()
-                want = src.clone()
-                ref_fn(want)
-                got = sym
-            else:
-                fn()
-                ref_fn(src)
-                got, want = (mine if plan is not None or coll == 'reduce_scatter' else sym), out
-            ex.check()
-            ok = torch.allclose(got.float(), want.float(), rtol=3e-2, atol=3e-2)
-            if rank == 0:
-                print(json.dumps({'collective': coll, 'algo': algo, 'nranks': n, 'bytes': nbytes, 'matches_nccl': bool(ok)}),
-                      flush=True)
-        else:
-            iters = 50 if nbytes <= (1 << 22) else 10
-            ms = _timed(fn, iters, dist)
-            ex.check()
-            row = {'collective': coll, 'algo': algo, 'nranks': n, 'bytes': nbytes, 'time_us': round(ms * 1e3, 2),
-                   'algbw_gbs': round(nbytes / ms / 1e6, 2), 'busbw_gbs': round(nbytes * _bus_factor(coll, n) / ms / 1e6, 2)}
-            if args.nccl:
-                t = src.clone()
-                nccl_ms = _timed(lambda: ref_fn(t), iters, dist)
-                row['nccl_time_us'] = round(nccl_ms * 1e3, 2)
-                row['nccl_busbw_gbs'] = round(nbytes * _bus_factor(coll, n) / nccl_ms / 1e6, 2)
-            if rank == 0:
-                print(json.dumps(row), flush=True)
+        yield size
         size *= 4
+
+
+def main_from_args(args, check=False):
+    dtype = _DTYPES[args.dtype]
+    lo, hi = parse_size(args.min_bytes), parse_size(args.max_bytes)
+    suite = getattr(args, 'suite', False)
+    collectives = ['allreduce', 'allgather', 'alltoall', 'reduce_scatter'] if suite else [args.collective]
+    dist, comm, ex, rank, n = _setup(args, collectives, hi)
+    for coll in collectives:
+        mode = getattr(args, 'algo', 'auto')
+        if suite:
+            modes = ['direct', 'xml']
+        elif mode == 'auto':
+            modes = ['xml' if args.xml is not None else 'direct']
+        else:
+            modes = [mode]
+        for m in modes:
+            for size in _sizes(lo, hi):
+                # the suite verifies each (collective, algorithm) once per size before timing it
+                row = _one_size(dist, comm, ex, rank, n, coll, m, size, dtype, check or suite,
+                                (args.nccl and (not suite or m == 'direct')) if not check else False)
+                if row is not None and rank == 0:
+                    print(json.dumps(row), flush=True)
+    if suite and n > 2:
+        # launch-latency tuning aid: the one-shot kernel with fixed CTA counts
+        for size in (16 << 10, 64 << 10, 256 << 10):
+            for ctas in (1, 2, 4, 8, 16):
+                os.environ['MSCCL_ONESHOT_CTAS'] = str(ctas)
+                t = torch.zeros(size // 2, device='cuda', dtype=torch.bfloat16)
+                if size <= comm.ll_max_bytes:
+                    ms = _timed(lambda: ex.all_reduce(t, algorithm='oneshot'), 50, dist)
+                    if rank == 0:
+                        print(json.dumps({'tune': 'oneshot_ctas', 'bytes': size, 'ctas': ctas, 'time_us': round(ms * 1e3, 2)}),
+                              flush=True)
+        os.environ.pop('MSCCL_ONESHOT_CTAS', None)
     comm.close()
     dist.destroy_process_group()

@@ -170,3 +170,28 @@ def test_race_detection_catches_missing_dependency():
         it.set_input(1, torch.ones(2))
         it.run()
         raise AssertionError('schedule happened to be ordered')
+
+
+def test_copy_threadblocks_split_local_copies():
+    # the local copies of a rank spread over several threadblocks: same result, one copy step per block
+    from msccl.collectives import allgather
+    from msccl.instance import Instance
+    from msccl.interp import run_reference_check
+    from msccl.ncclize import ncclize
+    from msccl.path_encoding import PathEncoding
+    from msccl.topologies import fully_connected
+    from msccl.xml import load_xml
+    topo = fully_connected(4)
+    algo = PathEncoding(topo, allgather(4)).solve(Instance(1))
+    assert algo is not None
+    one = load_xml(ncclize(algo, instances=4))
+    many = load_xml(ncclize(algo, instances=4, copy_threadblocks=4))
+    assert run_reference_check(one) == 'pass' and run_reference_check(many) == 'pass'
+
+    def copy_blocks(ir):
+        return [sum(1 for tb in g.tbs if any(st.type == 'cpy' for st in tb.steps)) for g in ir.gpus]
+    assert copy_blocks(one) == [1] * 4
+    assert copy_blocks(many) == [4] * 4
+    for g in many.gpus:
+        cnts = sorted(st.cnt for tb in g.tbs for st in tb.steps if st.type == 'cpy')
+        assert cnts == [1, 1, 1, 1]
