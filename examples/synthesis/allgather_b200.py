@@ -4,12 +4,16 @@ and write the XML; run it with ``torchrun --nproc-per-node N -m msccl bench --co
     python examples/synthesis/allgather_b200.py --gpus 8 --instances 8 -o allgather_fc8.xml
 """
 import argparse
+import os
+import sys
 
-from msccl.collectives import allgather
-from msccl.instance import Instance
-from msccl.ncclize import ncclize
-from msccl.path_encoding import PathEncoding
-from msccl.topologies import fully_connected
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from msccl.collectives import allgather  # noqa: E402
+from msccl.instance import Instance  # noqa: E402
+from msccl.ncclize import ncclize  # noqa: E402
+from msccl.path_encoding import PathEncoding  # noqa: E402
+from msccl.topologies import fully_connected  # noqa: E402
 
 
 def main():
