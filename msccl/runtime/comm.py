@@ -140,7 +140,23 @@ class Communicator:
             self.mode = 'ipc'
         self._upload_tables()
         self.barrier()
+        try:
+            from msccl.runtime.liveness import Liveness
+            self.liveness = Liveness.from_default_store(group)
+        except Exception:      # noqa: BLE001 - a job without a rendezvous store simply has no host-side liveness
+            self.liveness = None
         return self
+
+    def require_peers(self, max_age=None):
+        """Host-side check before a launch: raises ``PeerLostError`` if a peer announced its departure
+        (or, with ``max_age``, stopped reporting).  A store round trip: call it between steps, not per kernel."""
+        if getattr(self, 'liveness', None) is not None:
+            self.liveness.require_all(max_age)
+
+    def leave(self, reason='left'):
+        """Tell the other ranks that this rank stops taking part (between steps, nothing in flight)."""
+        if getattr(self, 'liveness', None) is not None:
+            self.liveness.leave(reason)
 
     def _try_collectively(self, fn, arg):
         """Run ``fn`` on every rank; succeed only if all ranks succeeded."""

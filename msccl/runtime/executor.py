@@ -295,3 +295,7 @@ class Executor:
 
     def check(self):
         self.comm.check()
+
+    def require_peers(self, max_age=None):
+        """Raise ``PeerLostError`` before launching anything if a peer has left the job."""
+        self.comm.require_peers(max_age)

@@ -35,3 +35,16 @@ def test_fused_moe_kernels():
            '--master-addr', '127.0.0.1', '--master-port', '29631', os.path.join(ROOT, 'tests', 'mp_moe_worker.py')]
     run = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert run.returncode == 0 and 'FUSED_MOE_OK' in run.stdout, run.stdout[-3000:] + run.stderr[-3000:]
+
+
+def test_rank_leaves_between_steps():
+    # host-side failure detection on real ranks; NVLS off everywhere, plain peer loads/stores only
+    n = torch.cuda.device_count()
+    n = 4 if n >= 4 else 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0', MSCCL_NVLS='0')
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={n}',
+           '--master-addr', '127.0.0.1', '--master-port', '29641', os.path.join(ROOT, 'tests', 'mp_leave_worker.py')]
+    run = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    out = run.stdout + run.stderr
+    assert run.returncode == 0, out[-3000:]
+    assert f'LEFT {n - 1}' in out and all(f'DETECTED {r}' in out for r in range(n - 1)), out[-3000:]
