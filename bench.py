@@ -156,11 +156,25 @@ def run_ours(args):
         def step():
             ex.run(plan, bufs)
 
+        # end to end: the step's input arrives from pinned host memory in slices on a copy stream, and the
+        # program runs on slice c while slice c + 1 is still crossing PCIe (same public call, on views)
+        copy_stream = torch.cuda.Stream()
+        pieces = 4
+        piece = numel // pieces // 4096 * 4096
+        bounds = [(c * piece, numel if c == pieces - 1 else (c + 1) * piece) for c in range(pieces)]
+        arrived = [torch.cuda.Event() for _ in range(pieces)]
+
         def e2e_step():
-            bufs[0].copy_(pinned, non_blocking=True)
-            ex.run(plan, bufs)
+            main = torch.cuda.current_stream()
+            with torch.cuda.stream(copy_stream):
+                for c, (lo, hi) in enumerate(bounds):
+                    bufs[0][lo:hi].copy_(pinned[lo:hi], non_blocking=True)
+                    arrived[c].record(copy_stream)
+            for c, (lo, hi) in enumerate(bounds):
+                main.wait_event(arrived[c])
+                ex.run(plan, {r: bufs[r][lo:hi] for r in range(world)})
             result_host.copy_(bufs[0][:4096].float().sum().reshape(1), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            main.synchronize()
 
         factor = bus_factor(world)
         config.update({'parallelism': 'emulated 8 ranks on 1 GPU (ring program, 4 instances)', 'ranks': world,
@@ -181,11 +195,24 @@ def run_ours(args):
         def step():
             ex.all_reduce(buf, algorithm='twoshot')
 
+        copy_stream = torch.cuda.Stream()
+        pieces = 8
+        piece = numel // pieces // 4096 * 4096
+        bounds = [(c * piece, numel if c == pieces - 1 else (c + 1) * piece) for c in range(pieces)]
+        arrived = [torch.cuda.Event() for _ in range(pieces)]
+
         def e2e_step():
-            buf.copy_(pinned, non_blocking=True)
-            ex.all_reduce(buf)
+            # slices of the input cross PCIe on a copy stream while earlier slices are being reduced
+            main = torch.cuda.current_stream()
+            with torch.cuda.stream(copy_stream):
+                for c, (lo, hi) in enumerate(bounds):
+                    buf[lo:hi].copy_(pinned[lo:hi], non_blocking=True)
+                    arrived[c].record(copy_stream)
+            for c, (lo, hi) in enumerate(bounds):
+                main.wait_event(arrived[c])
+                ex.all_reduce(buf[lo:hi])
             result_host.copy_(buf[:4096].float().sum().reshape(1), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            main.synchronize()
 
         factor = bus_factor(world)
         config.update({'parallelism': f'{n} ranks, one process per GPU', 'ranks': world, 'bytes_per_rank': nbytes,
@@ -212,7 +239,8 @@ def run_ours(args):
                 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic', 'impl': 'msccl-b200',
                 'config': config, 'clocks': clocks,
                 'e2e': {'value': round(e2e_value, 3), 'unit': 'GB/s', 'ms_per_step': round(e2e_ms, 5),
-                        'h2d_bytes_per_step': nbytes, 'd2h_bytes_per_step': 4},
+                        'h2d_bytes_per_step': nbytes, 'd2h_bytes_per_step': 4,
+                        'how': f'input in {pieces} slices on a copy stream, each reduced as soon as it has arrived'},
                 'gpu_launches': kernels_per_step * args.steps}
         if sweep:
             line['sweep'] = sweep
@@ -297,6 +325,18 @@ def run_reference(args):
             t_ms = _timed(n, iters, 5, lambda: dist.all_reduce(t), torch.cuda.synchronize)
             sweep.append({'bytes': size, 'us': round(t_ms * 1e3, 2),
                           'busbw_gbs': round(size * factor / (t_ms * 1e-3) / 1e9, 2)})
+    if n == 1:
+        # One GPU: this repo's arm runs an 8-rank program with all ranks emulated on the GPU.  The reference
+        # has no way to do that (its runtime is NCCL, which refuses two ranks on one device), and a 1-rank
+        # all-reduce moves no data, so there is no reference number for this configuration.  What the
+        # reference's path does with one rank is recorded for information only.
+        print(json.dumps({'impl': 'reference', 'unavailable': 'the reference runs collectives through NCCL, which cannot '
+                          'place the 8 ranks of this configuration on one GPU; its 1-rank all-reduce is an identity that '
+                          'moves no data', 'n_gpus': 1,
+                          'one_rank_identity': {'bytes': nbytes, 'ms_per_call': round(ms, 5), 'e2e_ms_per_step': round(e2e_ms, 5),
+                                                'note': note}, 'clocks': clocks}), flush=True)
+        dist.destroy_process_group()
+        return
     if rank == 0:
         line = {'metric': 'allreduce_busbw', 'value': round(nbytes * factor / (ms * 1e-3) / 1e9, 3), 'unit': 'GB/s',
                 'n_gpus': n, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': round(ms, 5),
