@@ -240,6 +240,14 @@ PYBIND11_MODULE(_msccl_native, m) {
                                       reinterpret_cast<int*>(error_words), max_ctas, as_stream(stream)),
              "launch of the block-scaled fp8 GEMM kernel");
   });
+  m.def("gemm_mxfp8_2cta", [](uintptr_t a, uintptr_t sfa, uintptr_t b, uintptr_t sfb, uintptr_t d, int M, int N, int K, int lda,
+                               int ldb, int ldd, uintptr_t error_words, int max_pairs, uintptr_t stream) {
+    check_rt(msccl::sm100::gemm_mxfp8_2cta(reinterpret_cast<const void*>(a), reinterpret_cast<const void*>(sfa),
+                                           reinterpret_cast<const void*>(b), reinterpret_cast<const void*>(sfb),
+                                           reinterpret_cast<void*>(d), M, N, K, lda, ldb, ldd,
+                                           reinterpret_cast<int*>(error_words), max_pairs, as_stream(stream)),
+             "launch of the two-CTA block-scaled fp8 GEMM kernel");
+  });
   // Fused all-gather -> GEMM (epilogue 0: plain, 1: SwiGLU).  heap_ptrs: every rank's heap base in this process.
   m.def("ag_gemm", [](uintptr_t x_local, uintptr_t b, uintptr_t d, int rows_per_rank, int N, int K, int ldb, int ldd, int rank,
                        int nranks, int comm_ctas, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs, size_t off_fused,

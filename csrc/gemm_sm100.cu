@@ -267,6 +267,22 @@ CUtensorMap make_u8_kmajor_map(const void* base, uint64_t rows, uint64_t cols, u
   return map;
 }
 
+// Tensor map over an array of 512-byte blocks (the packed scale factors): block i is row i of a
+// [blocks, 128] matrix of 32-bit words, box = one row, no swizzle.
+CUtensorMap make_block512_map(const void* base, uint64_t blocks) {
+  if (reinterpret_cast<uintptr_t>(base) % 16 != 0) throw std::runtime_error("TMA needs a 16-byte aligned base address");
+  CUtensorMap map;
+  cuuint64_t dims[2] = {128, blocks};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, 1};
+  cuuint32_t elem_strides[2] = {1, 1};
+  CUresult r = encode_fn()(&map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+  return map;
+}
+
 int sm_count() {
   static int count = 0;
   if (count == 0) {

@@ -44,7 +44,7 @@ def main():
         aq, sa = quantize_mxfp8(a.float())
         bq, sb = quantize_mxfp8(b.float())
         sa, sb = pack_mx_scales(sa), pack_mx_scales(sb)
-        ms = timed(lambda: gemm_mxfp8(aq, sa, bq, sb, out=out))
+        ms = timed(lambda: gemm_mxfp8(aq, sa, bq, sb, out=out, pair=None if args.pair < 0 else bool(args.pair)))
     else:
         ms = timed(lambda: gemm_bf16(a, b, out=out, bn=args.bn, epilogue='swiglu' if args.swiglu else 'none',
                                      pair=None if args.pair < 0 else bool(args.pair)))
@@ -52,7 +52,13 @@ def main():
     flops = 2.0 * args.m * args.n * args.k
     row = {'m': args.m, 'n': args.n, 'k': args.k, 'bn': 128 if args.fp8 else args.bn, 'swiglu': args.swiglu, 'fp8': args.fp8, 'pair': args.pair, 'us': round(ms * 1e3, 1),
            'tflops': round(flops / ms / 1e9, 1)}
-    if args.cublas:
+    if args.cublas and args.fp8:
+        # library reference for fp8: cuBLASLt through torch._scaled_mm with one scale per tensor
+        one = torch.ones((), device='cuda', dtype=torch.float32)
+        bt = bq.t()
+        ms_c = timed(lambda: torch._scaled_mm(aq, bt, scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+        row.update({'cublaslt_fp8_us': round(ms_c * 1e3, 1), 'cublaslt_fp8_tflops': round(flops / ms_c / 1e9, 1)})
+    elif args.cublas:
         full = torch.empty(args.m, args.n, device='cuda', dtype=torch.bfloat16)
         ms_c = timed(lambda: torch.matmul(a, b.t(), out=full))
         row.update({'cublas_us': round(ms_c * 1e3, 1), 'cublas_tflops': round(flops / ms_c / 1e9, 1)})

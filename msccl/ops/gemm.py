@@ -103,23 +103,26 @@ def dequantize_mxfp8(q, scales):
     return q.float() * s
 
 
-def pack_mx_scales(scales):
+def pack_mx_scales(scales, row_multiple=256):
     """Arrange ``scales`` [R, K / 32] (K % 128 == 0) the way the kernel's tensor-memory copy consumes them:
     one 512-byte block per (128 rows, 128 K elements), byte ``(r % 32) * 16 + (r // 32) * 4 + j`` of a block
-    = scale of row ``r`` for K elements ``[32 j, 32 j + 32)``.  Rows are padded to a multiple of 128 with
+    = scale of row ``r`` for K elements ``[32 j, 32 j + 32)``.  Rows are padded to a multiple of
+    ``row_multiple`` (256: what the CTA-pair kernel reads; 128 is enough for the single-CTA kernel) with
     the scale 1.0.  Returns a flat uint8 tensor."""
     r, kb4 = scales.shape
-    assert kb4 % 4 == 0 and scales.dtype == torch.uint8
-    tiles = -(-r // 128)
+    assert kb4 % 4 == 0 and scales.dtype == torch.uint8 and row_multiple % 128 == 0
+    tiles = -(-r // row_multiple) * (row_multiple // 128)
     padded = torch.full((tiles * 128, kb4), 127, dtype=torch.uint8, device=scales.device)
     padded[:r] = scales
     v = padded.view(tiles, 4, 32, kb4 // 4, 4)            # [tile, r // 32, r % 32, k block, j]
     return v.permute(0, 3, 2, 1, 4).contiguous().view(-1)
 
 
-def gemm_mxfp8(a, sfa_packed, b, sfb_packed, out=None, max_ctas=0, stream=None):
+def gemm_mxfp8(a, sfa_packed, b, sfb_packed, out=None, max_ctas=0, stream=None, pair=None):
     """``a``: [M, K] e4m3, ``b``: [N, K] e4m3, scales packed by ``pack_mx_scales``.  Returns bf16 [M, N] =
-    dequant(a) @ dequant(b).T with the scaling done inside the tensor core (tcgen05 block_scale MMA)."""
+    dequant(a) @ dequant(b).T with the scaling done inside the tensor core (tcgen05 block_scale MMA).
+    ``pair``: CTA pairs with 256 x 256 tiles (needs N % 256 == 0 and A scales padded to 256 rows);
+    ``None`` uses them whenever the operands allow it (``MSCCL_GEMM_PAIR=0`` turns that off)."""
     assert a.is_cuda and b.is_cuda and a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     m, k = a.shape
@@ -128,13 +131,24 @@ def gemm_mxfp8(a, sfa_packed, b, sfb_packed, out=None, max_ctas=0, stream=None):
     if k % 128 or n % 128:
         raise ValueError(f'K and N must be multiples of 128 (got K={k}, N={n})')
     need_a, need_b = -(-m // 128) * (k // 128) * 512, (n // 128) * (k // 128) * 512
-    if sfa_packed.numel() != need_a or sfb_packed.numel() != need_b:
-        raise ValueError(f'packed scales must hold {need_a} and {need_b} bytes')
+    need_a_pair = -(-m // 256) * 2 * (k // 128) * 512
+    if sfa_packed.numel() not in (need_a, need_a_pair) or sfb_packed.numel() < need_b:
+        raise ValueError(f'packed scales must hold {need_a} (or {need_a_pair}) and {need_b} bytes')
+    can_pair = n % 256 == 0 and sfa_packed.numel() == need_a_pair
+    if pair is None:
+        pair = can_pair and os.environ.get('MSCCL_GEMM_PAIR', '1') == '1'
+    if pair and not can_pair:
+        raise ValueError('the CTA-pair kernel needs N % 256 == 0 and A scales packed with row_multiple=256')
     assert sfa_packed.dtype == torch.uint8 and sfb_packed.dtype == torch.uint8 and sfa_packed.is_contiguous()
     if out is None:
         out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
     assert out.shape == (m, n) and out.stride(1) == 1 and out.dtype == torch.bfloat16
     stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+    if pair:
+        load().gemm_mxfp8_2cta(a.data_ptr(), sfa_packed.data_ptr(), b.data_ptr(), sfb_packed.data_ptr(), out.data_ptr(), m, n,
+                               k, a.stride(0), b.stride(0), out.stride(0), _errors(a.device).data_ptr(), (max_ctas + 1) // 2,
+                               stream_h)
+        return out
     load().gemm_mxfp8(a.data_ptr(), sfa_packed.data_ptr(), b.data_ptr(), sfb_packed.data_ptr(), out.data_ptr(), m, n, k,
                       a.stride(0), b.stride(0), out.stride(0), _errors(a.device).data_ptr(), max_ctas, stream_h)
     return out

@@ -56,6 +56,7 @@ class Executor:
         self.table = {}            # collective -> [(min_bytes, max_bytes, DevicePlan)]
         self.launches = 0          # kernels launched by this executor (for reporting)
         self._checked_grid = {}
+        self._ctx_cache = {}       # emulated mode: buffer pointers of all ranks -> device copy of the rank table
 
     # ------------------------------------------------------------------ plans
     def compile(self, algo_or_xml) -> DevicePlan:
@@ -150,12 +151,20 @@ class Executor:
         if plan.grid > self._checked_grid[key]:
             raise PlanError(f'{plan.grid} threadblocks cannot be co-resident on this device '
                             f'(limit {self._checked_grid[key]})')
+        rankctx = comm.dev_rankctx
         if comm.emulated_mode:
-            nat.upload_into(comm.dev_rankctx, comm.rankctx_bytes(buffers), stream_h)
+            # the per-rank buffer table lives on the device, one copy per distinct set of buffers: a
+            # host-to-device copy per launch would queue behind any large input copy in flight
+            table = tuple(buffers[r] for r in comm.local_ranks)
+            rankctx = self._ctx_cache.get(table)
+            if rankctx is None:
+                if len(self._ctx_cache) >= 64:
+                    nat.device_free(self._ctx_cache.pop(next(iter(self._ctx_cache))))
+                rankctx = self._ctx_cache[table] = nat.upload(comm.rankctx_bytes(buffers))
             b = (0, 0, 0)
         else:
             b = buffers[comm.rank]
-        nat.launch(plan.dev_tbs, plan.dev_steps, comm.dev_rankctx, chunk, tile, plan.slot_bytes, iterations,
+        nat.launch(plan.dev_tbs, plan.dev_steps, rankctx, chunk, tile, plan.slot_bytes, iterations,
                    comm.world, comm.timeout_ns, 0, plan.grid, key[0], key[1], stream_h, True,
                    not comm.emulated_mode, b[0], b[1], b[2])
         self.launches += 1

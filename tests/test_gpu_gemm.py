@@ -63,7 +63,7 @@ def test_gemm_strided_operands_and_few_ctas():
     assert torch.all(out[:, :256] == 0) and torch.all(out[:, 768:] == 0)
 
 
-@pytest.mark.parametrize('m,n,k', [(128, 128, 128), (256, 256, 512), (300, 384, 1024), (1024, 2048, 2048)])
+@pytest.mark.parametrize('m,n,k', [(128, 128, 128), (256, 256, 512), (300, 384, 1024), (300, 512, 256), (1024, 2048, 2048)])
 def test_gemm_mxfp8_block_scaled(m, n, k):
     # block-scaled fp8 (one power-of-two scale per 32 K elements of a row, applied by the tensor core)
     # against the fp32 product of the dequantised operands; rows and K blocks get widely different
@@ -80,8 +80,13 @@ def test_gemm_mxfp8_block_scaled(m, n, k):
 
     aq, sa = quantize_mxfp8(operand(m))
     bq, sb = quantize_mxfp8(operand(n))
-    d = gemm_mxfp8(aq, pack_mx_scales(sa), bq, pack_mx_scales(sb))
+    d = gemm_mxfp8(aq, pack_mx_scales(sa), bq, pack_mx_scales(sb), pair=False)
     check_gemm_errors()
+    if n % 256 == 0:
+        # CTA pairs (cta_group::2 block-scaled MMA): same products, same order within a tile row
+        d2 = gemm_mxfp8(aq, pack_mx_scales(sa), bq, pack_mx_scales(sb), pair=True)
+        check_gemm_errors()
+        assert torch.equal(d2, d)
     want = dequantize_mxfp8(aq, sa) @ dequantize_mxfp8(bq, sb).t()
     err = (d.float() - want).abs().max().item()
     scale = want.abs().max().item()
