@@ -159,7 +159,7 @@ def run_ours(args):
         # end to end: the step's input arrives from pinned host memory in slices on a copy stream, and the
         # program runs on slice c while slice c + 1 is still crossing PCIe (same public call, on views)
         copy_stream = torch.cuda.Stream()
-        pieces = 4
+        pieces = 2          # measured 1 / 2 / 4 / 8 slices: 9.0 / 8.6 / 9.4 / 11.7 ms per step
         piece = numel // pieces // 4096 * 4096
         bounds = [(c * piece, numel if c == pieces - 1 else (c + 1) * piece) for c in range(pieces)]
         arrived = [torch.cuda.Event() for _ in range(pieces)]

@@ -56,6 +56,9 @@ class Executor:
         self.table = {}            # collective -> [(min_bytes, max_bytes, DevicePlan)]
         self.launches = 0          # kernels launched by this executor (for reporting)
         self._checked_grid = {}
+        # Threadblocks of a program wait on one another, so they are launched cooperatively (the driver
+        # guarantees co-residency).  MSCCL_EXEC_COOPERATIVE=0 is a diagnostic switch for an otherwise idle GPU.
+        self.cooperative = os.environ.get('MSCCL_EXEC_COOPERATIVE', '1') != '0'
         self._ctx_cache = {}       # emulated mode: buffer pointers of all ranks -> device copy of the rank table
 
     # ------------------------------------------------------------------ plans
@@ -165,7 +168,7 @@ class Executor:
         else:
             b = buffers[comm.rank]
         nat.launch(plan.dev_tbs, plan.dev_steps, rankctx, chunk, tile, plan.slot_bytes, iterations,
-                   comm.world, comm.timeout_ns, 0, plan.grid, key[0], key[1], stream_h, True,
+                   comm.world, comm.timeout_ns, 0, plan.grid, key[0], key[1], stream_h, self.cooperative,
                    not comm.emulated_mode, b[0], b[1], b[2])
         self.launches += 1
         return results
