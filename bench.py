@@ -258,10 +258,7 @@ def sweep_ours(ex, comm, n, dtype, sizes=None):
     sizes = sizes or [1 << s for s in range(10, 29, 2)]
     for nbytes in sizes:
         numel = nbytes // 2
-        if nbytes <= comm.ll_max_bytes:
-            t = torch.zeros(numel, device='cuda', dtype=dtype)
-        else:
-            t = comm.tensor_at(comm.rank, comm.off_arena, numel, dtype)
+        t = comm.tensor_at(comm.rank, comm.off_arena, numel, dtype)      # symmetric: every path can take it
         iters = 50 if nbytes <= (1 << 20) else 10
         ms = _timed(n, iters, 5, lambda: ex.all_reduce(t), ex.check)
         rows.append({'bytes': nbytes, 'us': round(ms * 1e3, 2), 'busbw_gbs': round(nbytes * bus_factor(n) / (ms * 1e-3) / 1e9, 2)})

@@ -29,9 +29,9 @@ cudaError_t launch_twoshot_allreduce(char* const* heap_bases, char* mc_base, lon
 cudaError_t launch_push(const void* src, bool same_src, char* const* heap_bases, char* mc_base, long long dst_offset,
                         long long block_bytes, int rank, int nranks, SyncPage* const* syncs, unsigned long long timeout_ns,
                         int ctas, cudaStream_t stream);
-cudaError_t launch_oneshot_allreduce(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes,
-                                     int dtype, int rank, int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas,
-                                     cudaStream_t stream);
+cudaError_t launch_oneshot(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes, int dtype,
+                           int rank, int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas, int mode,
+                           cudaStream_t stream);
 }  // namespace msccl
 
 namespace {
@@ -346,13 +346,22 @@ PYBIND11_MODULE(_msccl_native, m) {
                                 reinterpret_cast<SyncPage* const*>(syncs_dev), timeout_ns, ctas, as_stream(stream)),
              "launch of the push kernel");
   });
-  // Out-of-place all-reduce of a small message through LL staging slots on every rank.
+  // One-shot LL collectives through staging slots on every rank (any device memory).
+  // mode: 0 all-reduce, 1 all-gather, 2 reduce-scatter, 3 all-to-all; `bytes` is the size of one block.
+  m.def("oneshot", [](uintptr_t in, uintptr_t out, uintptr_t staging_dev, long long bytes, long long slot_bytes, int dtype,
+                       int rank, int nranks, uintptr_t sync, unsigned long long timeout_ns, int ctas, int mode,
+                       uintptr_t stream) {
+    check_rt(msccl::launch_oneshot(reinterpret_cast<const void*>(in), reinterpret_cast<void*>(out),
+                                   reinterpret_cast<char* const*>(staging_dev), bytes, slot_bytes, dtype, rank, nranks,
+                                   reinterpret_cast<SyncPage*>(sync), timeout_ns, ctas, mode, as_stream(stream)),
+             "launch of the one-shot LL kernel");
+  });
   m.def("oneshot_allreduce", [](uintptr_t in, uintptr_t out, uintptr_t staging_dev, long long bytes, long long slot_bytes,
                                  int dtype, int rank, int nranks, uintptr_t sync, unsigned long long timeout_ns, int ctas,
                                  uintptr_t stream) {
-    check_rt(msccl::launch_oneshot_allreduce(reinterpret_cast<const void*>(in), reinterpret_cast<void*>(out),
-                                             reinterpret_cast<char* const*>(staging_dev), bytes, slot_bytes, dtype, rank,
-                                             nranks, reinterpret_cast<SyncPage*>(sync), timeout_ns, ctas, as_stream(stream)),
+    check_rt(msccl::launch_oneshot(reinterpret_cast<const void*>(in), reinterpret_cast<void*>(out),
+                                   reinterpret_cast<char* const*>(staging_dev), bytes, slot_bytes, dtype, rank, nranks,
+                                   reinterpret_cast<SyncPage*>(sync), timeout_ns, ctas, 0, as_stream(stream)),
              "launch of the one-shot all-reduce kernel");
   });
 }

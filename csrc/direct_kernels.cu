@@ -1,8 +1,9 @@
 // Direct (non-interpreted) all-reduce kernels over symmetric memory for one NVSwitch box.
 //
-//   one-shot LL  : every rank pushes its whole message into a private staging slot on every
-//                  peer as 16-byte {data, flag, data, flag} packets and then sums the n slots in
-//                  rank order.  One NVLink traversal, no barrier, no fence: the latency floor
+//   one-shot LL  : every rank pushes its message (all-reduce, all-gather) or one block per peer
+//                  (reduce-scatter, all-to-all) into a private staging slot on the peer as 16-byte
+//                  {data, flag, data, flag} packets; the receiver sums the n slots in rank order or
+//                  copies them out.  One NVLink traversal, no barrier, no fence: the latency floor
 //                  for small messages.  Input and output may be ordinary device memory.
 //   two-shot     : in place on a symmetric buffer.  Rank r owns 1/n of the message: it reduces
 //                  that slice across all ranks and publishes the result to all ranks.
@@ -233,11 +234,18 @@ push_kernel(const char* src, char* const* heap_bases, char* mc, long long dst_of
 
 // ---- one-shot LL ---------------------------------------------------------------------------
 // staging[r] = rank r's staging area as mapped here: [2 parities][nranks senders][slot_bytes],
-// slot_bytes >= 2 * message bytes (a packet carries 8 bytes of payload per 16).
-template <typename T>
+// slot_bytes >= 2 * block bytes (a packet carries 8 bytes of payload per 16).
+// One kernel shape serves four collectives on blocks of `bytes`:
+//   PER_PEER false: my one block goes to every rank          (all-reduce, all-gather)
+//   PER_PEER true : block p of my input goes to rank p        (reduce-scatter, all-to-all)
+//   SUM true      : out[v]       = sum over senders, in rank order   (all-reduce, reduce-scatter)
+//   SUM false     : out[s][v]    = what sender s sent                (all-gather, all-to-all)
+// No barrier and no fence: the flag travels inside every 16-byte packet.  Input and output may be
+// ordinary device memory.
+template <typename T, bool PER_PEER, bool SUM>
 __global__ void __launch_bounds__(kDirectThreads, 1)
-oneshot_ll_allreduce_kernel(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes,
-                            int rank, int nranks, SyncPage* sync, unsigned long long timeout_ns) {
+oneshot_ll_kernel(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes, int rank, int nranks,
+                  SyncPage* sync, unsigned long long timeout_ns) {
   __shared__ int s_fail;
   if (threadIdx.x == 0) s_fail = 0;
   __syncthreads();
@@ -249,18 +257,28 @@ oneshot_ll_allreduce_kernel(const void* in, void* out, char* const* staging, lon
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
 
-  // push: my vector v goes to slot [parity][rank] of every rank (including myself)
+  // push: vector v of the block for rank p goes to slot [parity][rank] of p (including myself)
   for (long long v = tid; v < vectors; v += nthreads) {
-    const uint4 d = *reinterpret_cast<const uint4*>(static_cast<const char*>(in) + v * 16);
-    const uint4 p0 = make_uint4(d.x, flag, d.y, flag), p1 = make_uint4(d.z, flag, d.w, flag);
-    for (int r = 0; r < nranks; ++r) {
-      uint4* pk = reinterpret_cast<uint4*>(staging[(rank + r) % nranks] + parity_off + rank * slot_bytes) + 2 * v;
-      st_volatile_v4(pk, p0);
-      st_volatile_v4(pk + 1, p1);
+    if (PER_PEER) {
+      for (int r = 0; r < nranks; ++r) {
+        const int p = (rank + r) % nranks;
+        const uint4 d = *reinterpret_cast<const uint4*>(static_cast<const char*>(in) + (static_cast<long long>(p) * vectors + v) * 16);
+        uint4* pk = reinterpret_cast<uint4*>(staging[p] + parity_off + rank * slot_bytes) + 2 * v;
+        st_volatile_v4(pk, make_uint4(d.x, flag, d.y, flag));
+        st_volatile_v4(pk + 1, make_uint4(d.z, flag, d.w, flag));
+      }
+    } else {
+      const uint4 d = *reinterpret_cast<const uint4*>(static_cast<const char*>(in) + v * 16);
+      const uint4 p0 = make_uint4(d.x, flag, d.y, flag), p1 = make_uint4(d.z, flag, d.w, flag);
+      for (int r = 0; r < nranks; ++r) {
+        uint4* pk = reinterpret_cast<uint4*>(staging[(rank + r) % nranks] + parity_off + rank * slot_bytes) + 2 * v;
+        st_volatile_v4(pk, p0);
+        st_volatile_v4(pk + 1, p1);
+      }
     }
   }
-  // pull: sum the n slots of my own staging area in rank order.  All slots of a vector are polled
-  // together (the loads overlap); only slots whose flags have not arrived yet are read again.
+  // pull from the n slots of my own staging area.  All slots of a vector are polled together (the
+  // loads overlap); only slots whose flags have not arrived yet are read again.
   const char* mine = staging[rank] + parity_off;
   for (long long v = tid; v < vectors; v += nthreads) {
     constexpr int R8 = 8;
@@ -290,7 +308,8 @@ oneshot_ll_allreduce_kernel(const void* in, void* out, char* const* staging, lon
       for (int r = 0; r < R8; ++r) {
         if (r < nranks) {
           const uint4 d = make_uint4(a[r].x, a[r].z, b[r].x, b[r].z);
-          acc = (r == 0) ? d : Vec16<T>::add(acc, d);
+          if (SUM) acc = (r == 0) ? d : Vec16<T>::add(acc, d);
+          else *reinterpret_cast<uint4*>(static_cast<char*>(out) + (static_cast<long long>(r) * vectors + v) * 16) = d;
         }
       }
     } else {
@@ -308,10 +327,11 @@ oneshot_ll_allreduce_kernel(const void* in, void* out, char* const* staging, lon
           }
         }
         const uint4 d = make_uint4(pa.x, pa.z, pb.x, pb.z);
-        acc = (r == 0) ? d : Vec16<T>::add(acc, d);
+        if (SUM) acc = (r == 0) ? d : Vec16<T>::add(acc, d);
+        else *reinterpret_cast<uint4*>(static_cast<char*>(out) + (static_cast<long long>(r) * vectors + v) * 16) = d;
       }
     }
-    *reinterpret_cast<uint4*>(static_cast<char*>(out) + v * 16) = acc;
+    if (SUM) *reinterpret_cast<uint4*>(static_cast<char*>(out) + v * 16) = acc;
   }
   // the last CTA to finish advances the epoch
   __syncthreads();
@@ -337,11 +357,17 @@ cudaError_t twoshot_typed(char* const* heap_bases, char* mc_base, long long offs
   return cudaGetLastError();
 }
 
+// mode: 0 all-reduce, 1 all-gather, 2 reduce-scatter, 3 all-to-all
 template <typename T>
 cudaError_t oneshot_typed(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes, int rank,
-                          int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas, cudaStream_t stream) {
-  oneshot_ll_allreduce_kernel<T><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync,
-                                                                     timeout_ns);
+                          int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas, int mode, cudaStream_t stream) {
+  switch (mode) {
+    case 0: oneshot_ll_kernel<T, false, true><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns); break;
+    case 1: oneshot_ll_kernel<T, false, false><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns); break;
+    case 2: oneshot_ll_kernel<T, true, true><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns); break;
+    case 3: oneshot_ll_kernel<T, true, false><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns); break;
+    default: return cudaErrorInvalidValue;
+  }
   return cudaGetLastError();
 }
 
@@ -379,14 +405,16 @@ cudaError_t launch_push(const void* src, bool same_src, char* const* heap_bases,
   return cudaGetLastError();
 }
 
-cudaError_t launch_oneshot_allreduce(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes,
-                                     int dtype, int rank, int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas,
-                                     cudaStream_t stream) {
+// One-shot LL collectives on blocks of `bytes` (mode: 0 all-reduce, 1 all-gather, 2 reduce-scatter, 3 all-to-all).
+cudaError_t launch_oneshot(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes, int dtype,
+                           int rank, int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas, int mode,
+                           cudaStream_t stream) {
   if (bytes % 16 != 0 || 2 * bytes > slot_bytes || ctas < 1 || nranks > kMaxRanks) return cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(in) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0) return cudaErrorInvalidValue;
   switch (dtype) {
-    case DT_F32: return oneshot_typed<float>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns, ctas, stream);
-    case DT_BF16: return oneshot_typed<__nv_bfloat16>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns, ctas, stream);
-    case DT_F16: return oneshot_typed<__half>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns, ctas, stream);
+    case DT_F32: return oneshot_typed<float>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns, ctas, mode, stream);
+    case DT_BF16: return oneshot_typed<__nv_bfloat16>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns, ctas, mode, stream);
+    case DT_F16: return oneshot_typed<__half>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns, ctas, mode, stream);
     default: return cudaErrorInvalidValue;
   }
 }

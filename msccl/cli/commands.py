@@ -299,9 +299,10 @@ def make_run(subparsers):
         parser.add_argument('--nccl', action='store_true', help='also time torch.distributed (NCCL) on the same sizes')
         parser.add_argument('--suite', action='store_true',
                             help='all four collectives, direct kernels and registered plans, each verified against NCCL')
-        parser.add_argument('--algo', default='auto', choices=['auto', 'direct', 'xml'],
-                            help='all-gather / reduce-scatter / all-to-all: direct kernels on symmetric memory, or '
-                                 'the registered MSCCL-IR plan through the interpreter (auto: xml if --xml is given)')
+        parser.add_argument('--algo', default='auto', choices=['auto', 'oneshot', 'twoshot', 'direct', 'xml'],
+                            help='auto: size-based dispatch (one-shot LL, then kernels on symmetric memory); oneshot / twoshot '
+                                 '(all-reduce) / direct: one native kernel; xml: the registered MSCCL-IR plan through the '
+                                 'interpreter (also what auto means when --xml is given)')
 
     def handle(args):
         if args.command not in ('run', 'bench'):

@@ -84,32 +84,32 @@ def _one_size(dist, comm, ex, rank, n, coll, mode, size, dtype, check, nccl):
             if ex.select('allreduce', nbytes) is None:
                 return None
         else:
-            fn = lambda: ex.all_reduce(sym)                                            # noqa: E731
+            fn = lambda: ex.all_reduce(sym, algorithm=mode)                            # noqa: E731
         ref_fn = lambda t: dist.all_reduce(t)                                          # noqa: E731
-        algo = 'auto' if mode != 'xml' else ex.select('allreduce', nbytes).algo.name
+        algo = mode if mode != 'xml' else ex.select('allreduce', nbytes).algo.name
     else:
         if mode == 'xml':
             plan = ex.select(coll, nbytes if coll != 'allgather' else nbytes // n)
             if plan is None:
                 return None
-        algo = plan.algo.name if plan is not None else 'direct'
+        algo = plan.algo.name if plan is not None else mode
         sym = comm.tensor_at(comm.rank, comm.off_arena, numel, dtype)       # symmetric side of the direct kernels
         if coll == 'allgather':
             src = torch.randn(numel // n, device='cuda', generator=gen).to(dtype)
             out = torch.empty(numel, device='cuda', dtype=dtype)
             ref_fn = lambda t: dist.all_gather_into_tensor(out, t)                    # noqa: E731
-            direct = lambda: ex.all_gather(sym, src, algorithm='direct')              # noqa: E731
+            direct = lambda: ex.all_gather(sym, src, algorithm=mode)              # noqa: E731
         elif coll == 'reduce_scatter':
             src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
             out = torch.empty(numel // n, device='cuda', dtype=dtype)
             ref_fn = lambda t: dist.reduce_scatter_tensor(out, t)                     # noqa: E731
             sym.copy_(src)
-            direct = lambda: ex.reduce_scatter(mine, sym, algorithm='direct')         # noqa: E731
+            direct = lambda: ex.reduce_scatter(mine, sym, algorithm=mode)         # noqa: E731
         else:
             src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
             out = torch.empty(numel, device='cuda', dtype=dtype)
             ref_fn = lambda t: dist.all_to_all_single(out, t)                         # noqa: E731
-            direct = lambda: ex.all_to_all(sym, src, algorithm='direct')              # noqa: E731
+            direct = lambda: ex.all_to_all(sym, src, algorithm=mode)              # noqa: E731
         mine = torch.empty_like(out)
         if plan is not None:
             fn = lambda: ex.run(plan, src, mine)                                       # noqa: E731
@@ -138,6 +138,8 @@ def _one_size(dist, comm, ex, rank, n, coll, mode, size, dtype, check, nccl):
     iters = 50 if nbytes <= (1 << 22) else 10
     ms = _timed(fn, iters, dist)
     ex.check()
+    if plan is None and mode == 'auto' and ex.last_algorithm:
+        row['algo'] = ex.last_algorithm                      # what the size-based dispatch picked
     row.update({'time_us': round(ms * 1e3, 2), 'algbw_gbs': round(nbytes / ms / 1e6, 2),
                 'busbw_gbs': round(nbytes * _bus_factor(coll, n) / ms / 1e6, 2)})
     if nccl:
@@ -164,16 +166,16 @@ def main_from_args(args, check=False):
     for coll in collectives:
         mode = getattr(args, 'algo', 'auto')
         if suite:
-            modes = ['direct', 'xml']
-        elif mode == 'auto':
-            modes = ['xml' if args.xml is not None else 'direct']
+            modes = ['auto', 'xml']
+        elif mode == 'auto' and args.xml is not None:
+            modes = ['xml']
         else:
             modes = [mode]
         for m in modes:
             for size in _sizes(lo, hi):
                 # the suite verifies each (collective, algorithm) once per size before timing it
                 row = _one_size(dist, comm, ex, rank, n, coll, m, size, dtype, check or suite,
-                                (args.nccl and (not suite or m == 'direct')) if not check else False)
+                                (args.nccl and (not suite or m == 'auto')) if not check else False)
                 if row is not None and rank == 0:
                     print(json.dumps(row), flush=True)
     if suite and n > 2:

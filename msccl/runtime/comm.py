@@ -120,8 +120,8 @@ class Communicator:
         self.local_ranks = [self.rank]
         self.device = torch.cuda.current_device()
         if ll_max_bytes is None:
-            # one-shot sends (n-1) copies of the message: worthwhile up to ~2 MB of total traffic
-            ll_max_bytes = max(256 << 10, (2 << 20) // self.world)
+            # largest block of the one-shot LL kernels: worthwhile while a rank moves up to ~4 MB in total
+            ll_max_bytes = max(512 << 10, (4 << 20) // self.world)
         self._set_layout(self.world, ll_max_bytes, fifo_bytes, arena_bytes)
         mode = mode or os.environ.get('MSCCL_SYMM', 'auto')
         errors = []

@@ -59,6 +59,7 @@ class Executor:
         # Threadblocks of a program wait on one another, so they are launched cooperatively (the driver
         # guarantees co-residency).  MSCCL_EXEC_COOPERATIVE=0 is a diagnostic switch for an otherwise idle GPU.
         self.cooperative = os.environ.get('MSCCL_EXEC_COOPERATIVE', '1') != '0'
+        self.last_algorithm = None  # what the last collective call dispatched to
         self._ctx_cache = {}       # emulated mode: buffer pointers of all ranks -> device copy of the rank table
 
     # ------------------------------------------------------------------ plans
@@ -186,12 +187,14 @@ class Executor:
             return tensor
         offset = comm.heap_offset_of(tensor)
         if algorithm == 'auto':
-            if nbytes <= comm.ll_max_bytes and nbytes % 16 == 0:
+            # one-shot all-reduce sends n - 1 copies of the whole message: half the gather-type limit
+            if nbytes <= min(comm.ll_max_bytes, max(256 << 10, (2 << 20) // comm.world)) and nbytes % 16 == 0:
                 algorithm = 'oneshot'
             elif offset is not None and nbytes % 16 == 0:
                 algorithm = 'twoshot'
             else:
                 algorithm = 'xml'
+        self.last_algorithm = algorithm
         if algorithm == 'oneshot':
             # one 16-byte vector per thread
             ctas = int(os.environ.get('MSCCL_ONESHOT_CTAS', '0')) or max(1, min(32, -(-nbytes // (16 * 512))))
@@ -230,6 +233,29 @@ class Executor:
             raise PlanError(f'no {collective} plan registered for {nbytes} bytes')
         return self.run(plan, inp.view(-1), out.view(-1) if out is not None else None, stream=stream)[self.comm.rank]
 
+    def _oneshot(self, mode, inp, out, block_bytes, stream):
+        """One-shot LL kernel on blocks of ``block_bytes`` (0 all-reduce, 1 all-gather, 2 reduce-scatter, 3 all-to-all)."""
+        comm = self.comm
+        ctas = int(os.environ.get('MSCCL_ONESHOT_CTAS', '0')) or max(1, min(32, -(-block_bytes // (16 * 512))))
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        comm.native.oneshot(inp.data_ptr(), out.data_ptr(), comm.dev_staging, block_bytes, comm.ll_slot_bytes,
+                            DTYPE_CODES[inp.dtype], comm.rank, comm.world, comm.sync_ptr(comm.rank), comm.timeout_ns, ctas, mode,
+                            stream_h)
+        self.launches += 1
+        return out
+
+    def _oneshot_ok(self, block_bytes, inp, out, may_alias):
+        if self.comm.emulated_mode or block_bytes > self.comm.ll_max_bytes or block_bytes % 16 or inp.dtype not in DTYPE_CODES:
+            return False
+        if inp.data_ptr() % 16 or out.data_ptr() % 16 or not (inp.is_contiguous() and out.is_contiguous()):
+            return False
+        if not may_alias:
+            a0, a1 = inp.data_ptr(), inp.data_ptr() + inp.numel() * inp.element_size()
+            b0, b1 = out.data_ptr(), out.data_ptr() + out.numel() * out.element_size()
+            if a0 < b1 and b0 < a1:
+                return False
+        return True
+
     def _direct_ctas(self, moved_bytes, cap=96):
         # one sweep of a CTA is 64 KB (512 threads x 8 vectors); half of that per CTA keeps mid sizes short
         return int(os.environ.get('MSCCL_DIRECT_CTAS', '0')) or max(1, min(cap, moved_bytes // (32 << 10)))
@@ -243,7 +269,17 @@ class Executor:
         nbytes = input.numel() * input.element_size()
         offset = None if comm.emulated_mode else comm.heap_offset_of(output)
         if algorithm == 'auto':
-            algorithm = 'direct' if offset is not None and nbytes % 16 == 0 and input.data_ptr() % 16 == 0 else 'xml'
+            if self._oneshot_ok(nbytes, input, output, may_alias=True) and output.numel() == input.numel() * comm.world:
+                algorithm = 'oneshot'  # latency-bound: flag-in-data packets, no barrier, any memory
+            elif offset is not None and nbytes % 16 == 0 and input.data_ptr() % 16 == 0:
+                algorithm = 'direct'
+            else:
+                algorithm = 'xml'
+        self.last_algorithm = algorithm
+        if algorithm == 'oneshot':
+            if not self._oneshot_ok(nbytes, input, output, may_alias=True):
+                raise PlanError(f'one-shot all-gather: blocks of at most {comm.ll_max_bytes} bytes, 16-byte aligned')
+            return self._oneshot(1, input, output, nbytes, stream)
         if algorithm == 'direct':
             if offset is None:
                 raise PlanError('the direct all-gather needs an output from Communicator.symmetric_empty')
@@ -265,9 +301,18 @@ class Executor:
         comm = self.comm
         nbytes = input.numel() * input.element_size()
         offset = None if comm.emulated_mode else comm.heap_offset_of(input)
+        out_bytes = output.numel() * output.element_size()
         if algorithm == 'auto':
             ok = offset is not None and nbytes % (16 * comm.world) == 0 and output.data_ptr() % 16 == 0
-            algorithm = 'direct' if ok else 'xml'
+            if self._oneshot_ok(out_bytes, input, output, may_alias=False) and out_bytes * comm.world == nbytes:
+                algorithm = 'oneshot'
+            else:
+                algorithm = 'direct' if ok else 'xml'
+        self.last_algorithm = algorithm
+        if algorithm == 'oneshot':
+            if not self._oneshot_ok(out_bytes, input, output, may_alias=False) or out_bytes * comm.world != nbytes:
+                raise PlanError(f'one-shot reduce-scatter: blocks of at most {comm.ll_max_bytes} bytes, no overlap of input and output')
+            return self._oneshot(2, input, output, out_bytes, stream)
         if algorithm == 'direct':
             if offset is None:
                 raise PlanError('the direct reduce-scatter needs an input from Communicator.symmetric_empty')
@@ -291,7 +336,16 @@ class Executor:
         offset = None if comm.emulated_mode else comm.heap_offset_of(output)
         if algorithm == 'auto':
             ok = offset is not None and nbytes % (16 * comm.world) == 0 and input.data_ptr() % 16 == 0
-            algorithm = 'direct' if ok else 'xml'
+            if nbytes % comm.world == 0 and self._oneshot_ok(nbytes // comm.world, input, output, may_alias=False) \
+                    and output.numel() == input.numel():
+                algorithm = 'oneshot'
+            else:
+                algorithm = 'direct' if ok else 'xml'
+        self.last_algorithm = algorithm
+        if algorithm == 'oneshot':
+            if nbytes % comm.world or not self._oneshot_ok(nbytes // comm.world, input, output, may_alias=False):
+                raise PlanError(f'one-shot all-to-all: blocks of at most {comm.ll_max_bytes} bytes, no overlap of input and output')
+            return self._oneshot(3, input, output, nbytes // comm.world, stream)
         if algorithm == 'direct':
             if offset is None:
                 raise PlanError('the direct all-to-all needs an output from Communicator.symmetric_empty')

@@ -156,6 +156,36 @@ def main():
     if rank == 0:
         print('direct all-gather / all-to-all / reduce-scatter: exact', flush=True)
 
+    # 3c. one-shot LL all-gather / all-to-all / reduce-scatter on ordinary memory (no barrier, flag in data)
+    for dtype in (torch.float32, torch.bfloat16):
+        for blk in (8, 2048, 40000):                       # elements per block; 40000 leaves a ragged last CTA
+            gen = torch.Generator().manual_seed(77 + blk)
+            full = [torch.randn(blk * n, generator=gen).to(dtype) for _ in range(n)]
+            for _ in range(3):                             # consecutive launches alternate the staging parity
+                mine = full[rank][:blk].cuda()
+                out = torch.zeros(blk * n, device='cuda', dtype=dtype)
+                ex.all_gather(out, mine, algorithm='oneshot')
+                ex.check()
+                assert torch.equal(out.cpu(), torch.cat([f[:blk] for f in full])), ('oneshot all_gather', dtype, blk)
+                src = full[rank].cuda()
+                ex.all_to_all(out, src, algorithm='oneshot')
+                ex.check()
+                assert torch.equal(out.cpu(), torch.cat([f[rank * blk:(rank + 1) * blk] for f in full])), ('oneshot all_to_all', dtype, blk)
+                red = torch.zeros(blk, device='cuda', dtype=dtype)
+                ex.reduce_scatter(red, src, algorithm='oneshot')
+                ex.check()
+                want = rank_order_sum([f[rank * blk:(rank + 1) * blk] for f in full], dtype)
+                assert torch.equal(red.cpu().view(torch.uint8), want.view(torch.uint8)), ('oneshot reduce_scatter', dtype, blk)
+    # auto dispatch picks the one-shot kernel for small blocks and still agrees
+    small = torch.full((1024,), float(rank + 1), device='cuda')
+    gathered = torch.empty(1024 * n, device='cuda')
+    ex.all_gather(gathered, small)
+    ex.check()
+    assert ex.last_algorithm == 'oneshot' and torch.equal(gathered.cpu().view(n, 1024)[:, 0], torch.arange(1, n + 1).float())
+    dist.barrier()
+    if rank == 0:
+        print('one-shot all-gather / all-to-all / reduce-scatter: exact', flush=True)
+
     # 4. dispatcher: registered XML for a tensor outside the arena
     ex.register(program('two_shot', AllReduce(n, n, True), lambda: allreduce_two_shot(n), 2, threadblock_policy=manual))
     big = parts[rank][: n * 65536 * 4].cuda()
