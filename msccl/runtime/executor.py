@@ -187,8 +187,7 @@ class Executor:
             return tensor
         offset = comm.heap_offset_of(tensor)
         if algorithm == 'auto':
-            # one-shot all-reduce sends n - 1 copies of the whole message: half the gather-type limit
-            if nbytes <= min(comm.ll_max_bytes, max(256 << 10, (2 << 20) // comm.world)) and nbytes % 16 == 0:
+            if nbytes <= comm.ll_max_bytes and nbytes % 16 == 0:
                 algorithm = 'oneshot'
             elif offset is not None and nbytes % 16 == 0:
                 algorithm = 'twoshot'
