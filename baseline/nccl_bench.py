@@ -3,7 +3,7 @@
 through torch.distributed, device-timed (CUDA events), max over ranks, nccl-tests conventions
 (busBW = algBW * 2(n-1)/n for all-reduce, * (n-1)/n for the others).
 
-    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 baseline/nccl_bench.py --out gpurun_out/nccl.json
+    torchrun --nproc-per-node 8 --master-addr 127.0.0.1 baseline/nccl_bench.py --out nccl.json
 """
 import argparse
 import json

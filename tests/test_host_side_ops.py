@@ -1,0 +1,72 @@
+"""CPU tests of the host-side helpers of the GPU ops: MX fp8 quantisation and scale packing
+(msccl/ops/gemm.py), tile geometry of the interpreter (msccl/runtime/plan.py)."""
+import pytest
+import torch
+
+from msccl.ops.gemm import dequantize_mxfp8, interleave_gate_up, pack_mx_scales, quantize_mxfp8
+
+
+def test_mxfp8_quantisation_error_and_scale_choice():
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(64, 256, generator=gen) * torch.exp2(torch.randint(-8, 8, (64, 1), generator=gen).float())
+    q, s = quantize_mxfp8(x)
+    assert q.dtype == torch.float8_e4m3fn and s.dtype == torch.uint8 and s.shape == (64, 8)
+    back = dequantize_mxfp8(q, s)
+    # e4m3 has 3 mantissa bits: relative error of a normal value at most 2^-4, measured against the block maximum
+    blocks = x.reshape(64, 8, 32)
+    err = (back.reshape(64, 8, 32) - blocks).abs().amax(dim=-1)
+    assert torch.all(err <= blocks.abs().amax(dim=-1) * 2.0 ** -4 + 1e-30)
+    # the scale is the smallest power of two that brings the block maximum into the e4m3 range
+    scaled_max = blocks.abs().amax(dim=-1) / torch.exp2(s.float() - 127)
+    assert torch.all(scaled_max <= 448.0) and torch.all(scaled_max > 224.0 - 1e-3)
+
+
+def test_mx_scale_packing_layout():
+    rows, kblocks = 300, 8                      # 300 rows -> 3 blocks of 128 (4 when padded to 256), K = 256
+    s = (torch.arange(rows * kblocks) % 251).to(torch.uint8).reshape(rows, kblocks)
+    for row_multiple, tiles in ((128, 3), (256, 4)):
+        p = pack_mx_scales(s, row_multiple)
+        assert p.numel() == tiles * (kblocks // 4) * 512
+        for r, kb in ((0, 0), (31, 3), (32, 4), (137, 5), (299, 7)):
+            tile, rr = divmod(r, 128)
+            k128, j = divmod(kb, 4)
+            off = (tile * (kblocks // 4) + k128) * 512 + (rr % 32) * 16 + (rr // 32) * 4 + j
+            assert p[off].item() == s[r, kb].item(), (r, kb)
+        # padding rows carry the scale 1.0
+        last = (tiles - 1) * (kblocks // 4) * 512
+        pad_row = tiles * 128 - 1 - (tiles - 1) * 128
+        assert p[last + (pad_row % 32) * 16 + (pad_row // 32) * 4].item() == 127
+
+
+def test_interleave_gate_up_groups_rows_per_tile():
+    g = torch.arange(256 * 4).float().reshape(256, 4)
+    u = -g
+    w = interleave_gate_up(g, u)
+    assert w.shape == (512, 4)
+    assert torch.equal(w[:128], g[:128]) and torch.equal(w[128:256], u[:128])
+    assert torch.equal(w[256:384], g[128:]) and torch.equal(w[384:], u[128:])
+
+
+def test_tile_geometry_pipelines_large_chunks():
+    from msccl.language import MSCCLProgram
+    from msccl.language.collectives import AllReduce
+    from msccl.programs.allreduce import allreduce_ring
+    from msccl.runtime.plan import PlanError, compile_plan, tile_geometry
+    from msccl.topologies import fully_connected
+    from msccl.xml import load_xml
+    prog = MSCCLProgram('ring', fully_connected(4), AllReduce(4, 4, True), 1)
+    with prog:
+        allreduce_ring(4, 1)
+    slot = 4 << 20
+    plan = compile_plan(load_xml(prog.generate_xml()), [0], slot)
+    # small chunk: one iteration
+    assert tile_geometry(plan, 1024, 2, slot) == (1024, 1)
+    # 8 MB chunk: cut into quarters (2 MB tiles) although a 4 MB slot would take half of it at once
+    tile, iters = tile_geometry(plan, 4 << 20, 2, slot)
+    assert iters == 4 and tile * 2 == 2 << 20
+    # 64 MB chunk: the slot size is the limit
+    tile, iters = tile_geometry(plan, 32 << 20, 2, slot)
+    assert tile * 2 * plan.max_cnt <= slot and iters * tile >= 32 << 20
+    # chunks must be whole 16-byte vectors
+    with pytest.raises(PlanError):
+        tile_geometry(plan, 500, 2, slot)
