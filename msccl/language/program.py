@@ -7,6 +7,9 @@ compiler lowers to MSCCL-IR.
 
 Parity: reference ``msccl/language/__init__.py:16-269``.
 """
+import os
+import sys
+import time
 from dataclasses import dataclass
 
 from msccl.language.compiler.schedule import auto_assign_tbs, manual_assign_tbs
@@ -46,6 +49,7 @@ class MSCCLProgram:
         self.buffers = collective.init_buffers()
         self.instr_dag = InstructionDAG(self.num_ranks, self.buffers)
         self._lowered = None
+        self.pass_times = {}          # compiler pass -> seconds (filled by lower / generate_xml)
         for rank in range(self.num_ranks):
             for index in range(len(self.buffers[rank][Buffer.input])):
                 buffer, where = collective.get_buffer_index(rank, Buffer.input, index)
@@ -99,28 +103,44 @@ class MSCCLProgram:
         return self.collective.check(self)
 
     # ------------------------------------------------------------ lowering
+    def _timed(self, name, fn, *args):
+        t0 = time.perf_counter()
+        out = fn(*args)
+        self.pass_times[name] = self.pass_times.get(name, 0.0) + time.perf_counter() - t0
+        return out
+
     def lower(self):
         dag = self.instr_dag
-        dag.convert_set_list()
+        self._timed('order edges', dag.convert_set_list)
         if self.instr_fusion:
-            dag.optimize()
-        dag._complete_metadata()
+            self._timed('fuse instructions', dag.optimize)
+        self._timed('chunk steps and priorities', dag._complete_metadata)
         if self.threadblock_policy == ThreadblockPolicy.manual:
-            manual_assign_tbs(dag)
+            self._timed('assign threadblocks (manual)', manual_assign_tbs, dag)
         else:
-            auto_assign_tbs(dag)
-        dag.lower_pt1(self.instances)
-        gpus = dag.lower_pt2(self.instances, self.interleaved_replication)
+            self._timed('assign threadblocks and channels', auto_assign_tbs, dag)
+        self._timed('infer dependencies, place scratch', dag.lower_pt1, self.instances)
+        gpus = self._timed('replicate instances', dag.lower_pt2, self.instances, self.interleaved_replication)
         if self.check_xml:
-            check_dependency_cycles(dag.tbs)
-            check_threadblock_ordering(dag)
+            self._timed('check dependency cycles', check_dependency_cycles, dag.tbs)
+            self._timed('check threadblock ordering', check_threadblock_ordering, dag)
         return Program(self.name, self.collective.name, self.collective.inplace, self.protocol, gpus)
 
     def generate_xml(self):
         # Lowering rewrites the instruction DAG in place, so it runs once and the text is kept.
         if self._lowered is None:
-            self._lowered = ir_to_xml(self.lower(), dependence_nop=self.dependence_nop)
+            program = self.lower()
+            self._lowered = self._timed('write XML', lambda: ir_to_xml(program, dependence_nop=self.dependence_nop))
+            if os.environ.get('MSCCL_PROFILE'):
+                print(self.format_pass_times(), file=sys.stderr)
         return self._lowered
+
+    def format_pass_times(self):
+        """Wall-clock seconds per compiler pass of the last lowering, one line per pass."""
+        total = sum(self.pass_times.values())
+        lines = [f'MSCCL: compile passes of {self.name} ({total * 1e3:.1f} ms)']
+        lines += [f'  {name:<36} {seconds * 1e3:9.2f} ms' for name, seconds in self.pass_times.items()]
+        return '\n'.join(lines)
 
     def to_dot(self):
         """Graphviz text of the instruction DAG (no rendering)."""

@@ -11,6 +11,7 @@ from fractions import Fraction
 
 from msccl.instance import Instance
 from msccl.synth.bounds import lower_bound_rounds, lower_bound_steps
+from msccl.synth.cache import active_cache
 from msccl.synth.smt_paths import PathEncoding
 
 
@@ -18,7 +19,17 @@ def _attempt(encoding, instance, logging):
     if logging:
         print(f'Solving instance {instance}... ', end='', flush=True)
     t0 = time.time()
-    algo = encoding.solve(instance)
+    cache = active_cache()
+    known = False
+    # the problem as the caller posed it (a combining collective is solved as its dual on the reversed topology)
+    topology = getattr(encoding, 'original_topology', encoding.topology)
+    collective = getattr(encoding, 'primal', encoding.collective)
+    if cache is not None:
+        known, algo = cache.lookup(topology, collective, instance)
+    if not known:
+        algo = encoding.solve(instance)
+        if cache is not None:
+            cache.store(topology, collective, instance, algo)
     if logging:
         verdict = 'synthesized!' if algo is not None else 'unsatisfiable.'
         print(f'{verdict} ({time.time() - t0:.1f}s)')

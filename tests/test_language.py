@@ -265,3 +265,22 @@ def test_dot_export():
         allgather_ring_inplace(2)
     text = prog.to_dot()
     assert text.startswith('digraph mscclang {') and '->' in text
+
+
+def test_compile_pass_times_are_recorded(monkeypatch, capsys):
+    from msccl.language import MSCCLProgram
+    from msccl.language.collectives import AllReduce
+    from msccl.programs.allreduce import allreduce_ring
+    from msccl.topologies import fully_connected
+    monkeypatch.setenv('MSCCL_PROFILE', '1')
+    prog = MSCCLProgram('timed_ring', fully_connected(4), AllReduce(4, 4, True), 2)
+    with prog:
+        allreduce_ring(4, 2)
+    xml = prog.generate_xml()
+    assert xml.startswith('<algo')
+    assert list(prog.pass_times)[:3] == ['order edges', 'fuse instructions', 'chunk steps and priorities']
+    assert 'write XML' in prog.pass_times and all(t >= 0 for t in prog.pass_times.values())
+    err = capsys.readouterr().err
+    assert 'MSCCL: compile passes of timed_ring' in err and 'assign threadblocks and channels' in err
+    prog.generate_xml()                                     # cached text: no second report
+    assert capsys.readouterr().err == ''

@@ -126,3 +126,38 @@ def test_gather_scatter_distributor_and_composer():
     assert ar.name == 'Allreduce(n=8)-DGX1-steps=4,rounds=6,chunks=2'
     with pytest.raises(ValueError):
         compose_allreduce(rs, PathEncoding(dgx1(), allgather(8)).solve(Instance(2)))
+
+
+def test_synthesis_cache_round_trip(tmp_path, monkeypatch, capsys):
+    # solved and unsatisfiable instances are stored once and answered from disk afterwards
+    from msccl.collectives import allgather, reduce_scatter
+    from msccl.instance import Instance
+    from msccl.serialization import load_msccl_object
+    from msccl.strategies import solve_instance
+    from msccl.synth import cache as synth_cache
+    from msccl.topologies import ring
+    monkeypatch.setenv('MSCCL_SYNTH_CACHE', str(tmp_path))
+    store = synth_cache.active_cache()
+    first = solve_instance(ring(4), allgather(4), Instance(2), logging=True)
+    assert first is not None and (store.hits, store.misses) == (0, 1)
+    files = list(tmp_path.iterdir())
+    assert len(files) == 1 and files[0].name.endswith('.msccl.json')
+    assert load_msccl_object(str(files[0])).name == first.name            # an ordinary algorithm file
+    again = solve_instance(ring(4), allgather(4), Instance(2), logging=True)
+    assert (store.hits, store.misses) == (1, 1)
+    assert [sorted(s.sends) for s in again.steps] == [sorted(s.sends) for s in first.steps]
+    assert capsys.readouterr().out.count('synthesized!') == 2              # same log lines either way
+    # unsatisfiable: one step is too few on a ring of four
+    assert solve_instance(ring(4), allgather(4), Instance(1)) is None
+    assert solve_instance(ring(4), allgather(4), Instance(1)) is None
+    assert (store.hits, store.misses) == (2, 2)
+    # a combining collective is keyed by the problem as posed, not by its dual
+    rs = solve_instance(ring(4), reduce_scatter(4), Instance(3))
+    assert rs is not None and solve_instance(ring(4), reduce_scatter(4), Instance(3)).name == rs.name
+    assert (store.hits, store.misses) == (3, 3)
+    # a damaged entry is solved again and replaced
+    files[0].write_text('{not json')
+    assert solve_instance(ring(4), allgather(4), Instance(2)) is not None
+    assert load_msccl_object(str(files[0])).name == first.name
+    monkeypatch.delenv('MSCCL_SYNTH_CACHE')
+    assert synth_cache.active_cache() is None
