@@ -1,0 +1,98 @@
+"""``torch.distributed``-shaped entry points backed by the native executor.
+
+    import torch.distributed as dist, msccl, msccl.torch as mt
+    dist.init_process_group('nccl'); torch.cuda.set_device(local_rank)
+    msccl.init('b200', 1, (msccl.Collective.allreduce, (0, None)))      # optional: registers MSCCL-IR plans
+    mt.init(arena_bytes=2 << 30)
+    grads = mt.symmetric_empty((n,), torch.bfloat16)                     # registered memory: every path can use it
+    mt.all_reduce(grads)
+
+The reference hands its plans to an NCCL fork and the application keeps calling ``torch.distributed``
+(reference README.md:20-38); here the same plan table (``MSCCL_CONFIG``) is installed into this
+process's ``Executor`` and the calls below dispatch by size and placement: one-shot LL kernels for small
+blocks, kernels on symmetric memory for large ones, the registered MSCCL-IR plan otherwise.  Sums only.
+"""
+import math
+import os
+
+import torch
+
+from msccl.runtime import Communicator, Executor
+
+_state = {'comm': None, 'executor': None}
+
+
+def init(group=None, arena_bytes=1 << 30, fifo_bytes=256 << 20, load_plans=True):
+    """Create this process's communicator and executor (collective: every rank of ``group`` calls it)."""
+    if _state['comm'] is not None:
+        raise RuntimeError('msccl.torch is already initialised; call shutdown() first')
+    comm = Communicator.from_process_group(group, fifo_bytes=fifo_bytes, arena_bytes=arena_bytes)
+    ex = Executor(comm)
+    if load_plans and os.environ.get('MSCCL_CONFIG'):
+        ex.load_plan_table()
+    _state.update(comm=comm, executor=ex)
+    return ex
+
+
+def is_initialized():
+    return _state['executor'] is not None
+
+
+def executor():
+    if _state['executor'] is None:
+        raise RuntimeError('call msccl.torch.init() after torch.distributed.init_process_group()')
+    return _state['executor']
+
+
+def communicator():
+    executor()
+    return _state['comm']
+
+
+def shutdown():
+    if _state['comm'] is not None:
+        _state['comm'].close()
+    _state.update(comm=None, executor=None)
+
+
+def symmetric_empty(shape, dtype=torch.bfloat16):
+    """A tensor in registered memory at the same offset on every rank (all ranks call this in the same order)."""
+    shape = (shape,) if isinstance(shape, int) else tuple(shape)
+    flat, _ = communicator().symmetric_empty(math.prod(shape), dtype)
+    return flat.view(shape)
+
+
+def all_reduce(tensor, stream=None):
+    """In-place sum over all ranks."""
+    if not tensor.is_contiguous():
+        raise ValueError('all_reduce needs a contiguous tensor')
+    executor().all_reduce(tensor.view(-1), stream=stream)
+    return tensor
+
+
+def all_gather_into_tensor(output, input, stream=None):
+    """``output`` = concatenation of every rank's ``input`` along dimension 0."""
+    executor().all_gather(output.view(-1), input.contiguous().view(-1), stream=stream)
+    return output
+
+
+def reduce_scatter_tensor(output, input, stream=None):
+    """``output`` = this rank's slice (along dimension 0) of the sum of every rank's ``input``."""
+    executor().reduce_scatter(output.view(-1), input.contiguous().view(-1), stream=stream)
+    return output
+
+
+def all_to_all_single(output, input, stream=None):
+    """Equal splits along dimension 0: slice ``s`` of ``output`` = slice ``rank`` of rank ``s``'s ``input``."""
+    executor().all_to_all(output.view(-1), input.contiguous().view(-1), stream=stream)
+    return output
+
+
+def check():
+    """Synchronise and raise if a kernel of this rank reported a timeout."""
+    executor().check()
+
+
+def require_peers(max_age=None):
+    """Host-side check before the next step: raises ``PeerLostError`` if a rank has left the job."""
+    executor().require_peers(max_age)

@@ -70,3 +70,37 @@ def test_tile_geometry_pipelines_large_chunks():
     # chunks must be whole 16-byte vectors
     with pytest.raises(PlanError):
         tile_geometry(plan, 500, 2, slot)
+
+
+def test_flat_gradients_bucket_views_and_reduction():
+    # gradients are views into flat buckets; the reduction callback sees whole buckets
+    from msccl.parallel.data_parallel import FlatGradients
+    model = torch.nn.Sequential(torch.nn.Linear(7, 5), torch.nn.Linear(5, 3))
+    allocated = []
+
+    def allocate(numel, dtype):
+        allocated.append(torch.full((numel,), 9.0, dtype=dtype))
+        return allocated[-1]
+
+    flat = FlatGradients(model.parameters(), allocate, bucket_bytes=200)
+    assert len(flat.buckets) >= 2 and all(t.numel() % 4 == 0 for t in allocated)          # 16-byte slots of fp32
+    assert all(torch.count_nonzero(t) == 0 for t in allocated)
+    model(torch.ones(2, 7)).sum().backward()
+    for p in model.parameters():
+        assert any(p.grad.data_ptr() >= t.data_ptr() and p.grad.data_ptr() < t.data_ptr() + t.numel() * 4 for t in allocated)
+    before = [p.grad.clone() for p in model.parameters()]
+    seen = []
+    flat.all_reduce_gradients(lambda t: seen.append(t.numel()) or t.mul_(4), world=4)      # "sum" of 4 equal ranks
+    assert seen == [t.numel() for t in allocated]
+    for p, b in zip(model.parameters(), before):
+        assert torch.allclose(p.grad, b)
+    model[0].weight.grad = torch.zeros_like(model[0].weight)                               # detached from the bucket
+    with pytest.raises(RuntimeError):
+        flat.all_reduce_gradients(lambda t: t, world=1)
+
+
+def test_msccl_torch_needs_init():
+    import msccl.torch as mt
+    assert not mt.is_initialized()
+    with pytest.raises(RuntimeError):
+        mt.all_reduce(torch.zeros(4))
