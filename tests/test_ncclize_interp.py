@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from msccl.collectives import allgather, allreduce, alltoall, reduce_scatter
+from msccl.collectives import allgather, alltoall, reduce_scatter
 from msccl.instance import Instance
 from msccl.interp import (DeadlockError, Interpreter, RaceError, run_algorithm, run_reference_check)
 from msccl.language import Buffer, MSCCLProgram, ThreadblockPolicy, chunk
