@@ -104,3 +104,38 @@ def test_msccl_torch_needs_init():
     assert not mt.is_initialized()
     with pytest.raises(RuntimeError):
         mt.all_reduce(torch.zeros(4))
+
+
+def test_route_top_k_renormalises():
+    from msccl.ops.moe import route_top_k
+    logits = torch.tensor([[0.0, 1.0, 2.0, 3.0], [5.0, 5.0, -9.0, -9.0]])
+    experts, weights = route_top_k(logits, topk=2)
+    assert experts.tolist()[0] == [3, 2] and sorted(experts.tolist()[1]) == [0, 1]
+    assert torch.allclose(weights.sum(dim=-1), torch.ones(2))
+    e = torch.exp(torch.tensor([3.0, 2.0]))
+    assert torch.allclose(weights[0], e / e.sum())
+
+
+def test_pipeline_handover_on_gloo_ranks():
+    import os
+    import socket
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        port = s.getsockname()[1]
+    world = 3
+    procs = [subprocess.Popen([sys.executable, os.path.join(here, 'mp_pipeline_worker.py')],
+                              env=dict(os.environ, MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port), RANK=str(r),
+                                       WORLD_SIZE=str(world), OMP_NUM_THREADS='1'),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    outs = []
+    for p in procs:
+        try:
+            outs.append(p.communicate(timeout=120)[0])
+        except subprocess.TimeoutExpired:
+            p.kill()
+            outs.append(p.communicate()[0])
+    assert [p.returncode for p in procs] == [0] * world, '\n'.join(outs)
+    assert all(f'PIPELINE_OK {r}' in outs[r] for r in range(world))
