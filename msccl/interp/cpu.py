@@ -12,7 +12,13 @@ Execution model (the contract the native executor implements as well):
   on the send connection; ``rrs`` pops, adds the local ``dst`` and pushes the sum without
   storing it; ``rrcs`` pops, adds, stores and pushes; ``cpy`` / ``re`` are local copy / add;
   ``nop`` only waits;
-* a FIFO holds at most ``fifo_depth`` messages - a sender blocks when it is full.
+* a FIFO holds at most ``fifo_depth`` messages - a sender blocks when it is full;
+* extension steps of the B200 runtime (never written by the classic tool chain): ``bar`` - the k-th
+  barrier of a channel on one GPU waits for the k-th barrier of that channel on every other GPU;
+  ``mmr`` - local ``dst`` = sum over all GPUs of their ``src`` slot; ``mmb`` - the local ``src`` is
+  stored into the ``dst`` slot of every GPU; ``mmar`` - the slot is replaced on every GPU by its sum over
+  all GPUs.  They model the in-switch (NVLS) reduction and multicast store: the sum is formed in fp32
+  and rounded once, whatever the number of GPUs.
 
 Scheduling is cooperative and deterministic; if no threadblock can advance the interpreter
 raises ``DeadlockError`` naming the blocked steps.  With ``race_check=True`` every access to a
@@ -84,6 +90,10 @@ class Interpreter:
         self.done_clock = {}                 # (rank, tb, step) -> clock snapshot after the step
         self.last_write = {}                 # (rank, buf, chunk) -> (tb key, time, description)
         self.reads_since = defaultdict(list)
+        # cross-rank barriers
+        self.bar_passed = defaultdict(int)   # tb key -> barriers passed
+        self.bar_arrived = defaultdict(dict)  # (channel, index) -> {rank: clock snapshot}
+        self.bar_progress = False            # set when a threadblock newly arrives at a barrier
 
     # ---------------------------------------------------------------- buffers
     def view(self, rank, buf, off, cnt):
@@ -138,6 +148,8 @@ class Interpreter:
         st = tb.steps[self.pc[key]]
         if st.depid != -1 and self.pc[(rank, st.depid)] <= st.deps:
             return False
+        if st.type == 'bar':
+            return self._try_barrier(key, tb, st)
         inbox = self.fifos[(tb.recv, rank, tb.chan)] if st.is_recv() else None
         outbox = self.fifos[(rank, tb.send, tb.chan)] if st.is_send() else None
         if inbox is not None and not inbox:
@@ -166,6 +178,24 @@ class Interpreter:
                 dst.copy_(dst + src)
             payload = None
         elif t == 'nop':
+            payload = None
+        elif t in ('mmr', 'mmb', 'mmar'):
+            everyone = range(self.algo.ngpus)
+            if t == 'mmb':
+                self._touch(key, rank, st.srcbuf, st.srcoff, st.cnt, False, what)
+                value = self.view(rank, st.srcbuf, st.srcoff, st.cnt).clone()
+            else:
+                for r in everyone:
+                    self._touch(key, r, st.srcbuf, st.srcoff, st.cnt, False, what)
+                total = sum(self.view(r, st.srcbuf, st.srcoff, st.cnt).float() for r in everyone)
+                value = total.to(self.dtype)
+            if t == 'mmr':
+                self._touch(key, rank, st.dstbuf, st.dstoff, st.cnt, True, what)
+                self.view(rank, st.dstbuf, st.dstoff, st.cnt).copy_(value)
+            else:
+                for r in everyone:
+                    self._touch(key, r, st.dstbuf, st.dstoff, st.cnt, True, what)
+                    self.view(r, st.dstbuf, st.dstoff, st.cnt).copy_(value)
             payload = None
         elif st.is_recv():
             received, msg_clock = inbox.popleft()
@@ -208,14 +238,38 @@ class Interpreter:
         self.pc[key] += 1
         return True
 
+    def _try_barrier(self, key, tb, st):
+        rank, tbid = key
+        meeting = (tb.chan, self.bar_passed[key])
+        here = self.bar_arrived[meeting]
+        if rank not in here:
+            if self.race_check:
+                self.clock[key].tick(key)
+                if st.depid != -1:
+                    self.clock[key].join(self.done_clock[(rank, st.depid, st.deps)])
+            here[rank] = self.clock[key].snapshot() if self.race_check else None
+            self.bar_progress = True
+        if len(here) < self.algo.ngpus:
+            return False
+        if self.race_check:
+            for other in here.values():          # everything before anyone's barrier is ordered before what follows
+                self.clock[key].join(other)
+            if st.hasdep:
+                self.done_clock[(rank, tbid, st.s)] = self.clock[key].snapshot()
+        self.bar_passed[key] += 1
+        self.pc[key] += 1
+        return True
+
     def run(self):
         pending = deque(k for k in self.pc if self.tbs[k].steps)
         stalled = 0
         while pending:
             key = pending.popleft()
             moved = False
+            self.bar_progress = False
             while self.pc[key] < len(self.tbs[key].steps) and self._try_step(key):
                 moved = True
+            moved = moved or self.bar_progress   # arriving at a barrier lets the others through
             if self.pc[key] < len(self.tbs[key].steps):
                 pending.append(key)
                 stalled = 0 if moved else stalled + 1

@@ -31,7 +31,18 @@ class DevicePlan:
         self.algo = algo
         if algo.ngpus != comm.world:
             raise PlanError(f'program is for {algo.ngpus} GPUs, communicator has {comm.world}')
+        from msccl.language.ext_nvls import classify
         from msccl.runtime.plan import fifo_index_tables
+        # A program made of in-switch steps (mmar / mmb / mmr between barriers) is not interpreted: it is
+        # exactly what one native kernel does, and Executor.run hands it to that kernel.
+        self.nvls_kind = classify(algo)
+        if self.nvls_kind is not None:
+            self.host = None
+            self.dev_tbs = self.dev_steps = 0
+            self.grid = 0
+            self.slot_bytes = 0
+            self.scratch = {}
+            return
         conns = max((len(t) for t in fifo_index_tables(algo).values()), default=0)
         slot = MAX_SLOT_BYTES if conns == 0 else min(MAX_SLOT_BYTES, comm.fifo_bytes // (conns * K_FIFO_SLOTS))
         self.slot_bytes = slot // 1024 * 1024
@@ -46,7 +57,8 @@ class DevicePlan:
 
     def close(self):
         for p in (self.dev_tbs, self.dev_steps):
-            self.comm.native.device_free(p)
+            if p:
+                self.comm.native.device_free(p)
         self.scratch = {}
 
 
@@ -99,6 +111,8 @@ class Executor:
         if torch.is_tensor(outputs):
             outputs = {comm.local_ranks[0]: outputs}
         outputs = outputs or {}
+        if plan.nvls_kind is not None:
+            return self._run_in_switch(plan, inputs, outputs, stream)
         first = inputs[comm.local_ranks[0]]
         dtype = first.dtype
         if dtype not in DTYPE_CODES:
@@ -173,6 +187,43 @@ class Executor:
                    not comm.emulated_mode, b[0], b[1], b[2])
         self.launches += 1
         return results
+
+    def _run_in_switch(self, plan, inputs, outputs, stream):
+        """A program of in-switch steps (``msccl.language.ext_nvls``) on the native kernel of the same shape."""
+        comm = self.comm
+        if comm.emulated_mode or not comm.mc_base:
+            raise PlanError('in-switch programs need one process per GPU and a communicator with NVLink multicast')
+        rank, world = comm.rank, comm.world
+        t_in = inputs[rank]
+        offset = comm.heap_offset_of(t_in)
+        nbytes = t_in.numel() * t_in.element_size()
+        if offset is None or not t_in.is_contiguous() or nbytes % (16 * world) or t_in.dtype not in DTYPE_CODES:
+            raise PlanError('in-switch programs need a contiguous tensor from Communicator.symmetric_empty whose size is '
+                            'a multiple of 16 bytes per rank')
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        code = DTYPE_CODES[t_in.dtype]
+        nat = comm.native
+        if plan.nvls_kind == 'allreduce':
+            nat.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, offset, nbytes, code, rank, world, comm.dev_syncs,
+                                  comm.timeout_ns, 8, stream_h)
+            result = t_in
+        elif plan.nvls_kind == 'allgather':            # in place: the own block already sits at its position
+            block = nbytes // world
+            nat.push_blocks(t_in.data_ptr() + rank * block, True, comm.dev_heap_bases, comm.mc_base, offset, block, rank,
+                            world, comm.dev_syncs, comm.timeout_ns, self._direct_ctas(nbytes), stream_h)
+            result = t_in
+        else:
+            out = outputs.get(rank)
+            if out is None:
+                out = torch.empty(t_in.numel() // world, dtype=t_in.dtype, device=t_in.device)
+            if out.numel() * world != t_in.numel() or not out.is_contiguous() or out.data_ptr() % 16:
+                raise PlanError('reduce-scatter output must hold 1/world of the input')
+            nat.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, offset, nbytes, code, rank, world, comm.dev_syncs,
+                                  comm.timeout_ns, 8, stream_h, out.data_ptr())
+            result = out
+        self.launches += 1
+        self.last_algorithm = f'in-switch {plan.nvls_kind}'
+        return {rank: result}
 
     # -------------------------------------------------------------- collectives
     def all_reduce(self, tensor, stream=None, algorithm='auto'):

@@ -104,6 +104,24 @@ def validate(algo: AlgoIR, max_problems=50):
             if received:
                 receivers[(tb.recv, gpu.id, tb.chan)].append((tb.id, received))
 
+    # cross-rank barriers: the k-th `bar` of a channel on one GPU meets the k-th `bar` of that channel on
+    # every other GPU, so each GPU needs the same number of them, issued by one threadblock per channel
+    bars = defaultdict(dict)                      # channel -> gpu -> [tb ids issuing bars] / count
+    for gpu in algo.gpus:
+        for tb in gpu.tbs:
+            n = sum(1 for st in tb.steps if st.type == 'bar')
+            if n:
+                bars[tb.chan].setdefault(gpu.id, []).append((tb.id, n))
+    for chan, per_gpu in sorted(bars.items()):
+        counts = {}
+        for g in range(algo.ngpus):
+            owners = per_gpu.get(g, [])
+            if len(owners) > 1:
+                report(f'gpu {g}: barriers of channel {chan} are issued by {len(owners)} threadblocks (must be one)')
+            counts[g] = sum(n for _, n in owners)
+        if len(set(counts.values())) > 1:
+            report(f'channel {chan}: barrier counts differ between gpus: {counts}')
+
     for conn in sorted(set(senders) | set(receivers)):
         s, r = senders.get(conn, []), receivers.get(conn, [])
         src, dst, chan = conn
@@ -132,6 +150,8 @@ def find_deadlock(algo: AlgoIR, fifo_depth=None):
     pc = {(g.id, tb.id): 0 for g in algo.gpus for tb in g.tbs}
     tbs = {(g.id, tb.id): tb for g in algo.gpus for tb in g.tbs}
     in_flight = defaultdict(int)
+    arrived = defaultdict(set)                    # (channel, barrier index) -> gpus that reached it
+    passed = defaultdict(int)                     # (gpu, tb) -> barriers already passed
     work = deque(pc)
     idle_rounds = 0
     while work and idle_rounds <= len(work):
@@ -143,6 +163,17 @@ def find_deadlock(algo: AlgoIR, fifo_depth=None):
             st = tb.steps[pc[key]]
             if st.depid != -1 and pc[(rank, st.depid)] <= st.deps:
                 break
+            if st.type == 'bar':
+                meeting = (tb.chan, passed[key])
+                if rank not in arrived[meeting]:
+                    arrived[meeting].add(rank)
+                    advanced = True               # arriving is progress: the others may now get through
+                if len(arrived[meeting]) < algo.ngpus:
+                    break
+                passed[key] += 1
+                pc[key] += 1
+                advanced = True
+                continue
             if st.is_recv() and in_flight[(tb.recv, rank, tb.chan)] == 0:
                 break
             if st.is_send() and fifo_depth is not None and in_flight[(rank, tb.send, tb.chan)] >= fifo_depth:

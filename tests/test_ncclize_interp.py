@@ -195,3 +195,40 @@ def test_copy_threadblocks_split_local_copies():
     for g in many.gpus:
         cnts = sorted(st.cnt for tb in g.tbs for st in tb.steps if st.type == 'cpy')
         assert cnts == [1, 1, 1, 1]
+
+
+@pytest.mark.parametrize('ranks,instances', [(2, 1), (4, 2), (8, 4)])
+def test_in_switch_extension_programs(ranks, instances):
+    # bar / mmar / mmb / mmr: validated, executed race-free by the CPU interpreter, recognised by the executor
+    from msccl.language.ext_nvls import allgather_nvls, allreduce_nvls, classify, reduce_scatter_nvls
+    from msccl.xml import load_xml
+    from msccl.xml.validator import validate
+    for build, coll in ((allreduce_nvls, 'allreduce'), (allgather_nvls, 'allgather'), (reduce_scatter_nvls, 'reduce_scatter')):
+        algo = load_xml(build(ranks, instances))
+        assert validate(algo) == []
+        assert classify(algo) == coll
+        assert run_reference_check(algo, race_check=True).startswith('pass')
+        assert sum(st.type == 'bar' for g in algo.gpus for tb in g.tbs for st in tb.steps) == 2 * ranks * instances
+
+
+def test_in_switch_sum_is_rounded_once_and_barriers_are_checked():
+    from msccl.language.ext_nvls import allreduce_nvls, classify
+    from msccl.xml import load_xml
+    from msccl.xml.validator import find_deadlock, validate
+    text = allreduce_nvls(4)
+    algo = load_xml(text)
+    # bf16: 256 + 1 + 1 + 1 is 259 -> 260 when summed in fp32 and rounded once; rounding after every addition gives 256
+    inputs = [torch.full((4 * 8,), v, dtype=torch.bfloat16) for v in (256.0, 1.0, 1.0, 1.0)]
+    out = run_algorithm(algo, inputs, 8, dtype=torch.bfloat16)
+    assert all(torch.all(o == 260.0) for o in out)
+    # a GPU that skips its first barrier: counts differ, and the others can never pass
+    broken = text.replace('<step s="0" type="bar"', '<step s="0" type="nop"', 1)
+    bad = load_xml(broken)
+    assert any('barrier counts differ' in p for p in validate(bad))
+    assert find_deadlock(bad)
+    assert classify(bad) is None
+    # a classic program is not mistaken for an in-switch one
+    ring = MSCCLProgram('ring', fully_connected(4), AllReduce(4, 4, True), 1)
+    with ring:
+        allreduce_ring(4, 1)
+    assert classify(load_xml(ring.generate_xml())) is None
