@@ -23,7 +23,7 @@ def main():
         algo = load_xml(build(ranks, instances))
         problems = validate(algo)
         verdict = run_reference_check(algo, race_check=True) if not problems else problems
-        print(f'{algo.name}: {algo.total_tbs()} threadblocks, {verdict}', file=sys.stderr)
+        print(f'{algo.name}: {sum(len(g.tbs) for g in algo.gpus)} threadblocks, {verdict}', file=sys.stderr)
     print(allreduce_nvls(ranks, instances))
 
 
