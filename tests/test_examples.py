@@ -76,3 +76,17 @@ def test_init_and_synthesis_examples_run(clean_env):
     run = subprocess.run([sys.executable, os.path.join(ROOT, 'examples', 'synthesis', 'allgather_pareto.py')],
                          capture_output=True, text=True)
     assert run.returncode == 0 and 'interpreter: pass' in run.stdout, run.stdout + run.stderr
+
+
+def test_in_switch_and_b200_synthesis_examples_run(tmp_path):
+    run = subprocess.run([sys.executable, os.path.join(ROOT, 'examples', 'runtime', 'in_switch_programs.py'), '4', '2'],
+                         capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr
+    assert run.stdout.startswith('<algo') and run.stderr.count('pass (race-free)') == 3
+    out = tmp_path / 'ag4.xml'
+    run = subprocess.run([sys.executable, os.path.join(ROOT, 'examples', 'synthesis', 'allgather_b200.py'), '--gpus', '4',
+                          '--instances', '2', '-o', str(out)], capture_output=True, text=True)
+    assert run.returncode == 0, run.stderr
+    from msccl.interp import run_reference_check
+    from msccl.xml import load_xml_file
+    assert run_reference_check(load_xml_file(str(out))) == 'pass'
