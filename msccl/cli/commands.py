@@ -258,6 +258,9 @@ def make_check(subparsers):
     parser.add_argument('xml', type=Path, nargs='+')
     parser.add_argument('--elems', type=int, default=0, help='elements per chunk for the numeric run (0: skip)')
     parser.add_argument('--race-check', action='store_true', help='prove every conflicting access pair is ordered')
+    parser.add_argument('--cost', default=None, metavar='SIZE',
+                        help='also print the depth of the longest dependent chain and a time estimate for a message of '
+                             'SIZE (e.g. 1MB) on one NVSwitch box')
 
     def handle(args):
         if args.command != 'check':
@@ -281,6 +284,15 @@ def make_check(subparsers):
                 if not verdict.startswith('pass'):
                     status = 1
             print(summary)
+            if args.cost is not None:
+                from msccl.utils.sizes import parse_size
+                from msccl.xml.analysis import estimate_us, summarize
+                figures = summarize(algo)
+                nbytes = parse_size(args.cost)
+                busiest = max(figures.sent_chunks, key=figures.sent_chunks.get)
+                print(f'{path}: longest chain {figures.depth} steps; gpu {busiest} sends {figures.sent_chunks[busiest]} chunks '
+                      f'from {figures.sending_tbs[busiest]} threadblocks; estimate for {args.cost}: '
+                      f'{estimate_us(algo, nbytes, summary=figures):.1f} us ({algo.proto})')
         sys.exit(status)
     return handle
 

@@ -232,3 +232,30 @@ def test_in_switch_sum_is_rounded_once_and_barriers_are_checked():
     with ring:
         allreduce_ring(4, 1)
     assert classify(load_xml(ring.generate_xml())) is None
+
+
+def test_program_summary_and_cost_estimate():
+    from msccl.xml.analysis import estimate_us, summarize
+    n = 8
+    prog = MSCCLProgram('ring', fully_connected(n), AllReduce(n, n, True), 1, threadblock_policy=ThreadblockPolicy.manual)
+    with prog:
+        allreduce_ring(n, 1)
+    algo = load_xml(prog.generate_xml())
+    s = summarize(algo)
+    # a ring all-reduce passes every chunk through 2 (n - 1) hops, one more step for the first local read
+    assert s.complete and 2 * (n - 1) <= s.depth <= 2 * (n - 1) + 1
+    assert set(s.sent_chunks.values()) == {2 * (n - 1)} and set(s.sending_tbs.values()) == {1}
+    small, large = estimate_us(algo, 8 << 10, summary=s), estimate_us(algo, 1 << 30, summary=s)
+    assert abs(small - s.depth * 2.5) < 1.0                        # latency term dominates
+    bytes_out = 2 * (n - 1) / n * (1 << 30)
+    assert abs(large - (s.depth * 2.5 + bytes_out / 50e3)) < 1.0   # one sending threadblock at 50 GB/s
+    # more instances: same depth, proportionally more sending threadblocks
+    prog4 = MSCCLProgram('ring4', fully_connected(n), AllReduce(n, n, True), 4, threadblock_policy=ThreadblockPolicy.manual)
+    with prog4:
+        allreduce_ring(n, 1)
+    s4 = summarize(load_xml(prog4.generate_xml()))
+    assert s4.depth == s.depth and set(s4.sending_tbs.values()) == {4}
+    # a program that cannot finish is reported as incomplete
+    from msccl.language.ext_nvls import allreduce_nvls
+    stuck = load_xml(allreduce_nvls(4).replace('<step s="0" type="bar"', '<step s="0" type="nop"', 1))
+    assert not summarize(stuck).complete
