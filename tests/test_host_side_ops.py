@@ -139,3 +139,50 @@ def test_pipeline_handover_on_gloo_ranks():
             outs.append(p.communicate()[0])
     assert [p.returncode for p in procs] == [0] * world, '\n'.join(outs)
     assert all(f'PIPELINE_OK {r}' in outs[r] for r in range(world))
+
+
+def test_compiled_plan_tables_are_consistent():
+    # the flat arrays the interpreter kernel reads: sizes, FIFO offsets agreed by both ends, dependency indices
+    import struct
+    from msccl.language import MSCCLProgram, ThreadblockPolicy
+    from msccl.language.collectives import AllReduce
+    from msccl.programs.allreduce import allreduce_ring
+    from msccl.runtime.plan import K_FIFO_SLOTS, K_MAX_RANKS, PlanError, compile_plan
+    from msccl.topologies import fully_connected
+    from msccl.xml import load_xml
+    n, slot = 4, 1 << 16
+    prog = MSCCLProgram('ring', fully_connected(n), AllReduce(n, n, True), 2, threadblock_policy=ThreadblockPolicy.manual)
+    with prog:
+        allreduce_ring(n, 2)
+    algo = load_xml(prog.generate_xml())
+    plan = compile_plan(algo, list(range(n)), slot)
+    tb_fmt, step_fmt = struct.Struct('<4h4i2i2q'), struct.Struct('<4B2h3i')
+    assert tb_fmt.size == 48 and step_fmt.size == 20
+    tbs = [tb_fmt.unpack_from(plan.tb_bytes, i * 48) for i in range(len(plan.tb_bytes) // 48)]
+    steps = [step_fmt.unpack_from(plan.step_bytes, i * 20) for i in range(len(plan.step_bytes) // 20)]
+    assert len(tbs) == algo.num_threadblocks() == plan.total_tbs() and len(steps) == algo.num_steps()
+    send_off, recv_off = {}, {}
+    for rank, tb_id, send_peer, recv_peer, chan, nsteps, first, tbs_in_rank, send_conn, recv_conn, s_off, r_off in tbs:
+        assert tbs_in_rank == len(algo.gpus[rank].tbs) and first + nsteps <= len(steps)
+        if send_peer >= 0:
+            assert send_conn == chan * K_MAX_RANKS + send_peer and s_off % (K_FIFO_SLOTS * slot) == 0
+            send_off[(rank, send_peer, chan)] = s_off
+        if recv_peer >= 0:
+            assert recv_conn == chan * K_MAX_RANKS + recv_peer
+            recv_off[(recv_peer, rank, chan)] = r_off
+        for code, sbuf, dbuf, hasdep, depid, deps, soff, doff, cnt in steps[first:first + nsteps]:
+            assert 0 <= code <= 8 and sbuf in (0, 1, 2) and dbuf in (0, 1, 2)
+            if depid >= 0:
+                assert depid < tbs_in_rank and 0 <= deps
+    # sender and receiver of a connection agree on where its slots are in the receiver's FIFO area
+    assert send_off == recv_off and len(send_off) > 0
+    # no two incoming connections of a rank share slots
+    for rank in range(n):
+        offs = [off for (src, dst, chan), off in recv_off.items() if dst == rank]
+        assert len(offs) == len(set(offs))
+    # in place: output chunks are addressed through the input buffer
+    assert all(plan.extents[r]['o'] == 0 and plan.extents[r]['i'] == n * 2 for r in range(n))
+    # in-switch steps are not for the interpreter kernel
+    from msccl.language.ext_nvls import allreduce_nvls
+    with pytest.raises(PlanError):
+        compile_plan(load_xml(allreduce_nvls(4)), [0], slot)
