@@ -288,14 +288,18 @@ class Executor:
         comm = self.comm
         ctas = int(os.environ.get('MSCCL_ONESHOT_CTAS', '0')) or max(1, min(32, -(-block_bytes // (16 * 512))))
         stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        # all-gather and all-to-all only move bits: any element type goes through the fp32 instance of the kernel
+        code = DTYPE_CODES[inp.dtype] if mode in (0, 2) else 0
         comm.native.oneshot(inp.data_ptr(), out.data_ptr(), comm.dev_staging, block_bytes, comm.ll_slot_bytes,
-                            DTYPE_CODES[inp.dtype], comm.rank, comm.world, comm.sync_ptr(comm.rank), comm.timeout_ns, ctas, mode,
+                            code, comm.rank, comm.world, comm.sync_ptr(comm.rank), comm.timeout_ns, ctas, mode,
                             stream_h)
         self.launches += 1
         return out
 
-    def _oneshot_ok(self, block_bytes, inp, out, may_alias):
-        if self.comm.emulated_mode or block_bytes > self.comm.ll_max_bytes or block_bytes % 16 or inp.dtype not in DTYPE_CODES:
+    def _oneshot_ok(self, block_bytes, inp, out, may_alias, sums=False):
+        if self.comm.emulated_mode or block_bytes > self.comm.ll_max_bytes or block_bytes % 16:
+            return False
+        if inp.dtype != out.dtype or (sums and inp.dtype not in DTYPE_CODES):
             return False
         if inp.data_ptr() % 16 or out.data_ptr() % 16 or not (inp.is_contiguous() and out.is_contiguous()):
             return False
@@ -354,13 +358,13 @@ class Executor:
         out_bytes = output.numel() * output.element_size()
         if algorithm == 'auto':
             ok = offset is not None and nbytes % (16 * comm.world) == 0 and output.data_ptr() % 16 == 0
-            if self._oneshot_ok(out_bytes, input, output, may_alias=False) and out_bytes * comm.world == nbytes:
+            if self._oneshot_ok(out_bytes, input, output, may_alias=False, sums=True) and out_bytes * comm.world == nbytes:
                 algorithm = 'oneshot'
             else:
                 algorithm = 'direct' if ok else 'xml'
         self.last_algorithm = algorithm
         if algorithm == 'oneshot':
-            if not self._oneshot_ok(out_bytes, input, output, may_alias=False) or out_bytes * comm.world != nbytes:
+            if not self._oneshot_ok(out_bytes, input, output, may_alias=False, sums=True) or out_bytes * comm.world != nbytes:
                 raise PlanError(f'one-shot reduce-scatter: blocks of at most {comm.ll_max_bytes} bytes, no overlap of input and output')
             return self._oneshot(2, input, output, out_bytes, stream)
         if algorithm == 'direct':

@@ -31,6 +31,7 @@ def main():
         dist.all_reduce(t)
     assert t[0].item() == n * n
     dist.barrier()
+    reporting = dist.new_group(list(range(n - 1)))   # the ranks that keep reporting in the 'silent' scenario
     if scenario == 'leave':
         if rank == last:
             live.leave('shutting down')
@@ -50,16 +51,18 @@ def main():
         assert gone == {last: 'ValueError: bad batch'}, gone
     elif scenario == 'silent':
         if rank == last:
-            time.sleep(3.0)                   # alive, but not reporting
+            time.sleep(4.5)                   # alive, but not reporting
             print(f'SILENT {rank}', flush=True)
             return
-        for _ in range(10):
+        for _ in range(16):
             live.beat()
             time.sleep(0.15)
-        quiet = live.silent(max_age=1.0)
+        live.beat()
+        dist.barrier(group=reporting)         # both reporting ranks have just reported
+        quiet = live.silent(max_age=1.5)
         assert list(quiet) == [last] and quiet[last].startswith('silent for'), quiet
     try:
-        live.require_all(max_age=1.0 if scenario == 'silent' else None)
+        live.require_all(max_age=1.5 if scenario == 'silent' else None)
     except PeerLostError as e:
         assert list(e.lost) == [last]
         print(f'DETECTED {rank}: {e}', flush=True)    # and the next collective is never started
