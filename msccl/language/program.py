@@ -49,6 +49,7 @@ class MSCCLProgram:
         self.buffers = collective.init_buffers()
         self.instr_dag = InstructionDAG(self.num_ranks, self.buffers)
         self._lowered = None
+        self.in_switch_ops = []       # (kind, rank, src buffer, src index, dst buffer, dst index, size), see ext_nvls
         self.pass_times = {}          # compiler pass -> seconds (filled by lower / generate_xml)
         for rank in range(self.num_ranks):
             for index in range(len(self.buffers[rank][Buffer.input])):
@@ -98,6 +99,10 @@ class MSCCLProgram:
         if name is not None and name not in self.buffers[rank]:
             self.buffers[rank][name] = BufferSlice(Buffer.scratch, name)
 
+    def _refuse_after_in_switch(self):
+        if self.in_switch_ops:
+            raise RuntimeError('copy/reduce steps cannot be mixed with in-switch steps in one program')
+
     def check(self):
         """True iff the symbolic buffers satisfy the collective's postcondition."""
         return self.collective.check(self)
@@ -128,6 +133,9 @@ class MSCCLProgram:
 
     def generate_xml(self):
         # Lowering rewrites the instruction DAG in place, so it runs once and the text is kept.
+        if self._lowered is None and self.in_switch_ops:
+            from msccl.language.ext_nvls import emit_in_switch_program
+            self._lowered = self._timed('write XML', emit_in_switch_program, self)
         if self._lowered is None:
             program = self.lower()
             self._lowered = self._timed('write XML', lambda: ir_to_xml(program, dependence_nop=self.dependence_nop))
@@ -209,6 +217,7 @@ class Ref(ChunkRef):
         chunks land in the same place on ``dst``; for a scratch buffer without index they are
         appended.  Returns the destination reference (None for a copy onto itself)."""
         prog = self.prog
+        prog._refuse_after_in_switch()
         prog.check_buffer_exists(dst, buffer)
         if index == -1 and buffer is None:
             buffer, index = self.buffer, self.index
@@ -233,6 +242,7 @@ class Ref(ChunkRef):
     def reduce(self, other_chunkref, sendtb=-1, recvtb=-1, ch=-1):
         """Fold ``other_chunkref`` into these chunks (self is the accumulator); returns self."""
         prog = self.prog
+        prog._refuse_after_in_switch()
         src, dst = other_chunkref.rank, self.rank
         assert prog.topo.link(src, dst) or src == dst, f'No link from {src} to {dst}'
         prog.apply_reduce(src, other_chunkref.buffer, other_chunkref.index,

@@ -284,3 +284,51 @@ def test_compile_pass_times_are_recorded(monkeypatch, capsys):
     assert 'MSCCL: compile passes of timed_ring' in err and 'assign threadblocks and channels' in err
     prog.generate_xml()                                     # cached text: no second report
     assert capsys.readouterr().err == ''
+
+
+def test_in_switch_steps_in_the_dsl():
+    # bar / mmar / mmb / mmr written through the DSL: Check(), XML, validator, interpreter, executor classification
+    from msccl.interp import run_reference_check
+    from msccl.language import Buffer, MSCCLProgram, chunk
+    from msccl.language.collectives import AllGather, AllReduce, ReduceScatter
+    from msccl.language.ext_nvls import (allreduce_nvls, classify, in_switch_allreduce, in_switch_broadcast,
+                                         in_switch_reduce)
+    from msccl.topologies import fully_connected
+    from msccl.xml import load_xml
+    from msccl.xml.validator import validate
+    n = 4
+    cases = ((AllReduce(n, n, True), lambda r: in_switch_allreduce(r, Buffer.input, r), 'allreduce'),
+             (AllGather(n, 1, True), lambda r: in_switch_broadcast(r, Buffer.output, r), 'allgather'),
+             (ReduceScatter(n, 1, False), lambda r: in_switch_reduce(r, Buffer.input, r, Buffer.output, 0), 'reduce_scatter'))
+    for instances in (1, 3):
+        for coll, step, kind in cases:
+            prog = MSCCLProgram(f'{kind}_in_switch', fully_connected(n), coll, instances)
+            with prog:
+                assert not prog.check()                       # nothing has moved yet
+                for r in range(n):
+                    step(r)
+                assert prog.check()
+            algo = load_xml(prog.generate_xml())
+            assert validate(algo) == [] and classify(algo) == kind
+            assert run_reference_check(algo, race_check=True) == 'pass (race-free)'
+            assert [len(g.tbs) for g in algo.gpus] == [instances] * n
+    # the DSL program and the ready-made builder describe the same steps
+    prog = MSCCLProgram('x', fully_connected(n), AllReduce(n, n, True), 2)
+    with prog:
+        for r in range(n):
+            in_switch_allreduce(r, Buffer.input, r)
+    mine, ready = load_xml(prog.generate_xml()), load_xml(allreduce_nvls(n, 2))
+    shape = lambda a: [[(tb.chan, [(st.type, st.srcbuf, st.srcoff, st.dstbuf, st.dstoff) for st in tb.steps]) for tb in g.tbs]  # noqa: E731
+                       for g in a.gpus]
+    assert shape(mine) == shape(ready)
+    # no mixing with classic steps, in either order
+    prog = MSCCLProgram('mixed', fully_connected(n), AllReduce(n, n, True), 1)
+    with prog:
+        in_switch_allreduce(0, Buffer.input, 0)
+        with pytest.raises(RuntimeError):
+            chunk(0, Buffer.input, 1).copy(1, Buffer.input, 1)
+    prog = MSCCLProgram('mixed2', fully_connected(n), AllReduce(n, n, True), 1)
+    with prog:
+        chunk(1, Buffer.input, 0).reduce(chunk(0, Buffer.input, 0))
+        with pytest.raises(RuntimeError):
+            in_switch_allreduce(0, Buffer.input, 1)
