@@ -339,7 +339,10 @@ class Executor:
                 raise PlanError('the direct all-gather needs an output from Communicator.symmetric_empty')
             if output.numel() != input.numel() * comm.world:
                 raise PlanError('all-gather output must hold one input per rank')
-            use_nvls = bool(comm.mc_base) and os.environ.get('MSCCL_PUSH_NVLS', '0') == '1'
+            # one multimem.st per vector instead of n - 1 peer stores: measured on 8 GPUs it is as fast as peer
+            # stores up to 16 MB in total (28 us at 4 MB, 50 us at 16 MB) and slower above (414 vs 391 us at 256 MB)
+            prefer_switch = comm.world > 2 and nbytes * comm.world <= (16 << 20)
+            use_nvls = bool(comm.mc_base) and os.environ.get('MSCCL_PUSH_NVLS', '1' if prefer_switch else '0') == '1'
             stream_h = (stream or torch.cuda.current_stream()).cuda_stream
             comm.native.push_blocks(input.data_ptr(), True, comm.dev_heap_bases, comm.mc_base if use_nvls else 0, offset, nbytes,
                                     comm.rank, comm.world, comm.dev_syncs, comm.timeout_ns,
