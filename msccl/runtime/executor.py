@@ -1,14 +1,22 @@
-"""Executor: runs MSCCL-IR programs and the direct all-reduce kernels on a ``Communicator``.
+"""Executor: runs MSCCL-IR programs and the direct kernels on a ``Communicator``.
 
-``Executor.run(plan, ...)`` launches the interpreter kernel for one compiled program.
-``Executor.all_reduce / all_gather / reduce_scatter / all_to_all`` pick a program from the plan
-table by message size (the ``<msccl_algos>`` table ``msccl.init`` writes, reference
-``msccl/autosynth/__init__.py:75-94``), or for all-reduce one of the direct kernels:
+``Executor.run(plan, ...)`` launches the interpreter kernel for one compiled program (a program made of
+in-switch steps, ``msccl.language.ext_nvls``, goes to the native multimem kernel instead).
+``Executor.all_reduce / all_gather / reduce_scatter / all_to_all`` dispatch by size and placement:
 
-* message <= ``comm.ll_max_bytes``         -> one-shot LL kernel (any device memory);
-* tensor inside the symmetric arena          -> two-shot in place (NVLS multimem when the heap is
-                                               bound to a multicast object, peer loads otherwise);
-* otherwise                                  -> the interpreter with the registered program.
+* blocks <= ``comm.ll_max_bytes``            -> one-shot LL kernel: flag-in-data packets, no barrier, any
+                                               device memory (all four collectives);
+* tensor inside the symmetric arena          -> all-reduce / reduce-scatter: two-shot (NVLS multimem when the
+                                               heap is bound to a multicast object, peer loads in rank order
+                                               otherwise); all-gather / all-to-all: stores straight into the
+                                               peers' output between two barriers;
+* otherwise                                  -> the interpreter with the program registered for that size (the
+                                               ``<msccl_algos>`` table ``msccl.init`` writes, reference
+                                               ``msccl/autosynth/__init__.py:75-94``).
+
+As with any collective library, every rank issues the same collectives in the same order, and calls on one
+communicator do not overlap in time (staging slots, FIFOs and barrier counters are shared between them).
+``last_algorithm`` tells which path the last call took.
 """
 import math
 import os
