@@ -9,7 +9,7 @@ import pytest
 from msccl.interp import run_reference_check
 from msccl.language import MSCCLProgram, ThreadblockPolicy
 from msccl.language.collectives import AllGather, AllReduce, AllToAll
-from msccl.programs import classic
+from msccl.programs import classic, multistage
 from msccl.programs.allreduce import allreduce_allpairs, allreduce_ring
 from msccl.programs.alltoall import alltoall_direct, alltoall_hierarchical, alltoall_three_step
 from msccl.topologies import fully_connected
@@ -44,6 +44,15 @@ CASES = [
      (16, 'Simple', 2, 8, 66, 66)),
     ('alltonext_backward', lambda: classic.AllToNext(16, 8, False, False), lambda: classic.alltonext(2, 8, False), 1, {},
      (16, 'Simple', 2, 8, 66, 66)),
+    # programs spanning several groups of GPUs: totals recorded from this compiler (the reference's scripts use
+    # other chunk factors and manual threadblocks, so its totals are not comparable)
+    ('multinode_allpairs_4x2', lambda: AllReduce(8, 4, True), lambda: multistage.allreduce_multinode_allpairs(4, 2), 1, {},
+     (8, 'Simple', 1, 4, 64, 168)),
+    ('two_pairs', lambda: AllReduce(4, 2, True), multistage.allreduce_two_pairs, 1, {}, (4, 'Simple', 1, 2, 16, 32)),
+    ('pipeline_ring_4', lambda: multistage.StageAllReduce(4, 4), lambda: multistage.pipeline_allreduce_ring(4, 2), 1, {},
+     (8, 'Simple', 2, 4, 24, 40)),
+    ('pipeline_allpairs_4', lambda: multistage.StageAllReduce(4, 4), lambda: multistage.pipeline_allreduce_allpairs(4), 1, {},
+     (8, 'Simple', 2, 4, 56, 76)),
 ]
 
 
@@ -62,7 +71,10 @@ def test_example_totals_and_execution(name, make_coll, body, instances, options,
 
 
 @pytest.mark.parametrize('script,args', [('allreduce_ring.py', '4 2 1'), ('custom_collective.py', ''),
-                                         ('alltonext.py', '2 1 --backward'), ('allgather_direct.py', '4 2')])
+                                         ('alltonext.py', '2 1 --backward'), ('allgather_direct.py', '4 2'),
+                                         ('allreduce_multinode_allpairs.py', '2 3 2'), ('allreduce_two_pairs.py', '2'),
+                                         ('pipeline_allreduce.py', '4 2 --channels 2'),
+                                         ('pipeline_allreduce.py', '3 1 --allpairs')])
 def test_example_scripts_run(script, args):
     run = subprocess.run([sys.executable, os.path.join(ROOT, 'examples', 'mscclang', script)] + args.split() + ['--execute'],
                          capture_output=True, text=True)
@@ -90,3 +102,42 @@ def test_in_switch_and_b200_synthesis_examples_run(tmp_path):
     from msccl.interp import run_reference_check
     from msccl.xml import load_xml_file
     assert run_reference_check(load_xml_file(str(out))) == 'pass'
+
+
+@pytest.mark.parametrize('body', ['ring', 'allpairs'])
+def test_pipeline_stage_allreduce_numbers(body):
+    # the custom collective is checked numerically here: every rank of stage 1 holds the sum of stage 0's inputs
+    import torch
+    from msccl.interp import Interpreter
+    size = 4
+    prog = MSCCLProgram('stage', fully_connected(2 * size), multistage.StageAllReduce(size, size), 2)
+    with prog:
+        if body == 'ring':
+            multistage.pipeline_allreduce_ring(size, 2)
+        else:
+            multistage.pipeline_allreduce_allpairs(size)
+        assert prog.check()
+    algo = load_xml(prog.generate_xml())
+    elems = 3
+    gen = torch.Generator().manual_seed(5)
+    inputs = [torch.randint(-9, 9, (size * 2 * elems,), generator=gen).float() for _ in range(2 * size)]
+    machine = Interpreter(algo, elems, race_check=True)
+    for r, data in enumerate(inputs):
+        machine.set_input(r, data)
+    machine.run()
+    want = sum(inputs[:size])
+    for t in range(size, 2 * size):
+        assert torch.equal(machine.buffers[t]['i'][:want.numel()], want)     # in place: the result is in the input buffer
+
+
+def test_collective_file_and_device_order_examples(tmp_path):
+    target = tmp_path / 'send.json'
+    run = subprocess.run([sys.executable, os.path.join(ROOT, 'examples', 'custom_collective_file.py'), str(target)],
+                         capture_output=True, text=True)
+    assert run.returncode == 0 and target.exists(), run.stderr
+    run = subprocess.run([sys.executable, '-m', 'msccl', 'solve', 'least-steps', 'DGX1', 'custom', '--collective-file',
+                          str(target), '--no-save'], capture_output=True, text=True, cwd=ROOT)
+    assert run.returncode == 0 and '2→' in run.stdout, run.stdout + run.stderr
+    run = subprocess.run([sys.executable, os.path.join(ROOT, 'examples', 'device_order.py'), '--demo'],
+                         capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.count('Permutation(') == 4, run.stdout + run.stderr
