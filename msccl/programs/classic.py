@@ -170,3 +170,21 @@ def alltonext(num_nodes, gpus_per_node=8, forward=True):
                 if rank(other, c) != nxt:                     # cross-node copy to the matching GPU, gathered below
                     piece = piece.copy(rank(other, c), tag, 0, ch=c % 2)
                 piece.copy(nxt, Buffer.output, piece.get_dst_index(), ch=c % 2)
+
+
+# ------------------------------------------------------------------------------ binomial tree
+def allreduce_binomial_tree(size, chunks=1):
+    """In-place all-reduce along a binomial tree rooted at rank 0: in round d every rank whose index has bit d
+    set (and no lower bit) is folded into the rank ``2^d`` below it, then the sum travels back down the same
+    edges.  ``2 ceil(log2 size)`` steps for any ``size``; ``chunks`` = chunk factor of the collective.
+    (The reference's ``examples/mscclang/allreduce_binomial_tree.py`` no longer runs against its own API.)"""
+    dist = 1
+    edges = []
+    while dist < size:
+        for child in range(dist, size, 2 * dist):
+            edges.append((child, child - dist))
+        dist *= 2
+    for child, parent in edges:                           # up: reduce into the parent
+        chunk(parent, Buffer.input, 0, chunks).reduce(chunk(child, Buffer.input, 0, chunks))
+    for child, parent in reversed(edges):                 # down: the parent's value replaces the child's
+        chunk(parent, Buffer.input, 0, chunks).copy(child, Buffer.input, 0)

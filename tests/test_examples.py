@@ -74,7 +74,8 @@ def test_example_totals_and_execution(name, make_coll, body, instances, options,
                                          ('alltonext.py', '2 1 --backward'), ('allgather_direct.py', '4 2'),
                                          ('allreduce_multinode_allpairs.py', '2 3 2'), ('allreduce_two_pairs.py', '2'),
                                          ('pipeline_allreduce.py', '4 2 --channels 2'),
-                                         ('pipeline_allreduce.py', '3 1 --allpairs')])
+                                         ('pipeline_allreduce.py', '3 1 --allpairs'),
+                                         ('allreduce_binomial_tree.py', '6 2')])
 def test_example_scripts_run(script, args):
     run = subprocess.run([sys.executable, os.path.join(ROOT, 'examples', 'mscclang', script)] + args.split() + ['--execute'],
                          capture_output=True, text=True)
