@@ -12,10 +12,42 @@ Parity: reference ``msccl/language/rank_dag.py:318-378``.
 from msccl.language.mscclir import Buffer, ChunkRef, Op, Threadblock
 
 
+def mixed_size_accesses(dag):
+    """Pairs of accesses to the input/output buffers that overlap without covering the same chunks, as
+    ``(rank, buffer, (index, size), (index, size))``.  Interleaved replication maps copy ``i`` of an access to
+    ``index * instances + i * size``: two accesses of different extent to the same chunks then give their
+    copy ``i`` different sub-chunks, and the dependency between them (kept per copy) no longer orders the data
+    they share."""
+    ranges = {}
+    for tbs in dag.tbs:
+        for tb in tbs.values():
+            for op in tb.ops:
+                for ref in (op.src, op.dst):
+                    if ref is not None and (ref.buffer is Buffer.input or ref.buffer is Buffer.output):
+                        ranges.setdefault((ref.rank, ref.buffer), set()).add((ref.index, ref.size))
+    clashes = []
+    for (rank, buffer), found in ranges.items():
+        ordered = sorted(found)
+        for a, (ia, sa) in enumerate(ordered):
+            for ib, sb in ordered[a + 1:]:
+                if ib >= ia + sa:
+                    break
+                clashes.append((rank, buffer, (ia, sa), (ib, sb)))
+    return clashes
+
+
 def replicate(dag, instances, interleaved):
     if instances == 1:
         dag.instanced_tbs = dag.tbs
         return
+    if interleaved:
+        clashes = mixed_size_accesses(dag)
+        if clashes:
+            rank, buffer, first, second = clashes[0]
+            raise RuntimeError(
+                f'interleaved replication needs every access to a chunk to have the same extent, but rank {rank} '
+                f'{buffer} is accessed as chunks [{first[0]}, {first[0] + first[1]}) and [{second[0]}, {second[0] + second[1]}) '
+                f'({len(clashes)} such pairs); use interleaved_replication=False for this program')
 
     def moved(ref, i):
         if ref is None:

@@ -134,3 +134,53 @@ def pipeline_allreduce_allpairs(size):
         for dst in range(size):
             if dst != owner:
                 chunk(owner + size, Buffer.input, owner).copy(dst + size, Buffer.input, owner)
+
+
+# ------------------------------------------------------------------ rows x columns
+def allreduce_2d(rows, cols):
+    """In-place all-reduce with ``chunk_factor = rows * cols`` on GPUs arranged in ``cols`` columns of ``rows``
+    GPUs (GPU id = column * rows + row), columns being the fast direction (NVLink) and rows the slow one (PCIe
+    or network): reduce-scatter inside the columns, reduce-scatter of the column results along the rows (only
+    1 / rows of the data crosses the slow links), all-gather along the rows, all-gather inside the columns.
+    Chunk ``i * cols + j`` is owned by row i after the first phase and by GPU (row i, column j) after the second.
+    (The reference's ``examples/mscclang/allreduce_a100_pcie_hierarchical.py`` fails its own ``Check()``.)"""
+    def gpu(row, col):
+        return col * rows + row
+
+    for col in range(cols):                               # 1. reduce-scatter inside every column
+        for owner_row in range(rows):
+            for src_row in range(rows):
+                if src_row != owner_row:
+                    for j in range(cols):
+                        idx = owner_row * cols + j
+                        chunk(gpu(owner_row, col), Buffer.input, idx).reduce(chunk(gpu(src_row, col), Buffer.input, idx))
+    for row in range(rows):                               # 2. reduce-scatter along every row
+        for j in range(cols):
+            idx = row * cols + j
+            for src_col in range(cols):
+                if src_col != j:
+                    chunk(gpu(row, j), Buffer.input, idx).reduce(chunk(gpu(row, src_col), Buffer.input, idx))
+    for row in range(rows):                               # 3. all-gather along every row
+        for j in range(cols):
+            idx = row * cols + j
+            for dst_col in range(cols):
+                if dst_col != j:
+                    chunk(gpu(row, j), Buffer.input, idx).copy(gpu(row, dst_col), Buffer.input, idx)
+    for col in range(cols):                               # 4. all-gather inside every column
+        for row in range(rows):
+            for dst_row in range(rows):
+                if dst_row != row:
+                    chunk(gpu(row, col), Buffer.input, row * cols, cols).copy(gpu(dst_row, col), Buffer.input, row * cols)
+
+
+def allgather_two_pairs():
+    """All-gather (``chunk_factor = 1``, not in place) on 4 GPUs made of two NVLink pairs: every GPU gives its
+    chunk to its partner and to one GPU of the other pair, which passes it on to its own partner, so each
+    chunk crosses the slow link between the pairs once."""
+    size = 4
+    for r in range(size):
+        mine = chunk(r, Buffer.input, 0)
+        mine.copy(r, Buffer.output, r)
+        mine.copy(r ^ 1, Buffer.output, r)
+        across = mine.copy((r + 2) % size, Buffer.output, r)
+        across.copy(((r + 2) % size) ^ 1, Buffer.output, r)
