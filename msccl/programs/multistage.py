@@ -184,3 +184,51 @@ def allgather_two_pairs():
         mine.copy(r ^ 1, Buffer.output, r)
         across = mine.copy((r + 2) % size, Buffer.output, r)
         across.copy(((r + 2) % size) ^ 1, Buffer.output, r)
+
+
+# ------------------------------------------------------------------ reduce inside groups, gather everywhere
+class ReduceGather(Collective):
+    """``groups`` groups of ``gpus_per_group`` GPUs; every GPU has ``gpus_per_group`` input chunks.  Output chunk
+    ``q * gpus_per_group + j`` of every GPU = sum over the GPUs of group q of their input chunk j.
+    A custom collective (``name`` stays 'custom').  (The reference's ``examples/mscclang/reducegather.py``
+    defines the same idea but no longer runs against its own API.)"""
+
+    def __init__(self, groups, gpus_per_group):
+        super().__init__(groups * gpus_per_group, 1, False)
+        self.groups, self.gpus_per_group = groups, gpus_per_group
+
+    def init_buffers(self):
+        return [{Buffer.input: [Chunk(r, j) for j in range(self.gpus_per_group)], Buffer.output: [None] * self.num_ranks}
+                for r in range(self.num_ranks)]
+
+    def expected(self, index):
+        q, j = divmod(index, self.gpus_per_group)
+        return ReduceChunk(-1, [Chunk(q * self.gpus_per_group + m, j) for m in range(self.gpus_per_group)])
+
+    def check(self, prog):
+        ok = True
+        for r in range(self.num_ranks):
+            for index in range(self.num_ranks):
+                got = prog.buffers[r][Buffer.output][index]
+                if got != self.expected(index):
+                    print(f'Rank {r} output chunk {index} is incorrect: given {got}')
+                    ok = False
+        return ok
+
+
+def reduce_gather(groups, gpus_per_group):
+    """``ReduceGather(groups, gpus_per_group)``: all-pairs reduce-scatter inside every group (member j sums
+    input chunk j of its group into its output slot), then every result is copied to every other GPU."""
+    g = gpus_per_group
+    for q in range(groups):
+        for j in range(g):
+            owner = q * g + j
+            slot = q * g + j
+            acc = chunk(owner, Buffer.input, j).copy(owner, Buffer.output, slot)
+            for m in range(g):
+                if m != j:
+                    acc.reduce(chunk(q * g + m, Buffer.input, j))
+    for owner in range(groups * g):
+        for dst in range(groups * g):
+            if dst != owner:
+                chunk(owner, Buffer.output, owner).copy(dst, Buffer.output, owner)

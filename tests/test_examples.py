@@ -57,6 +57,7 @@ CASES = [
      dict(interleaved_replication=False), None),
     ('allgather_two_pairs', lambda: AllGather(4, 1, False), multistage.allgather_two_pairs, 2, {}, None),
     ('binomial_tree_6', lambda: AllReduce(6, 1, True), lambda: classic.allreduce_binomial_tree(6), 2, {}, None),
+    ('reduce_gather_2x3', lambda: multistage.ReduceGather(2, 3), lambda: multistage.reduce_gather(2, 3), 2, {}, None),
 ]
 
 
@@ -161,3 +162,23 @@ def test_mixed_extents_are_refused_under_interleaved_replication():
     with single:
         multistage.allreduce_2d(3, 3)
     assert run_reference_check(load_xml(single.generate_xml()), 2, race_check=True) == 'pass (race-free)'
+
+
+def test_reduce_gather_numbers():
+    import torch
+    from msccl.interp import Interpreter
+    groups, g, elems = 2, 3, 2
+    prog = MSCCLProgram('rg', fully_connected(groups * g), multistage.ReduceGather(groups, g), 2)
+    with prog:
+        multistage.reduce_gather(groups, g)
+        assert prog.check()
+    algo = load_xml(prog.generate_xml())
+    gen = torch.Generator().manual_seed(1)
+    inputs = [torch.randint(-5, 5, (g * 2 * elems,), generator=gen).float() for _ in range(groups * g)]
+    machine = Interpreter(algo, elems, race_check=True)
+    for r, data in enumerate(inputs):
+        machine.set_input(r, data)
+    machine.run()
+    want = torch.cat([sum(inputs[q * g + m] for m in range(g)) for q in range(groups)])
+    for r in range(groups * g):
+        assert torch.equal(machine.buffers[r]['o'][:want.numel()], want)
