@@ -19,10 +19,11 @@ def parser(description, *positional):
     return ap
 
 
-def emit(name, collective, body, instances=1, protocol='Simple', manual=False, execute=False, **program_options):
+def emit(name, collective, body, instances=1, protocol='Simple', manual=False, execute=False, topology=None,
+         **program_options):
     """Compile ``body`` into MSCCL-IR, print the XML, report the symbolic check on stderr."""
     policy = ThreadblockPolicy.manual if manual else ThreadblockPolicy.auto
-    prog = MSCCLProgram(name, fully_connected(collective.num_ranks), collective, instances, protocol=protocol,
+    prog = MSCCLProgram(name, topology or fully_connected(collective.num_ranks), collective, instances, protocol=protocol,
                         threadblock_policy=policy, **program_options)
     with prog:
         body()

@@ -232,3 +232,33 @@ def reduce_gather(groups, gpus_per_group):
         for dst in range(groups * g):
             if dst != owner:
                 chunk(owner, Buffer.output, owner).copy(dst, Buffer.output, owner)
+
+
+# ------------------------------------------------------------------ DGX-1 machines, one chunk
+DGX1_PATH = (1, 3, 2, 6, 7, 5, 4, 0)      # a path through all 8 GPUs of a DGX-1 that only uses NVLink
+
+
+def allreduce_dgx1_chain(num_nodes=2):
+    """Latency-oriented in-place all-reduce of one chunk over ``num_nodes`` DGX-1 machines (topology
+    ``distributed_fully_connected(dgx1(), num_nodes, 1)``): the chunk is summed along an NVLink path through
+    each machine, the machines' sums are exchanged between the GPUs at the end of the paths and added, and the
+    result travels back along the paths.  (Same idea as the reference's ``examples/mscclang/allreduce_dgx1.py``,
+    which is written against an API the reference no longer has.)"""
+    def rank(node, step):
+        return DGX1_PATH[step] + 8 * node
+
+    last = len(DGX1_PATH) - 1
+    for node in range(num_nodes):                         # sum along the path
+        for step in range(1, last + 1):
+            chunk(rank(node, step), Buffer.input, 0).reduce(chunk(rank(node, step - 1), Buffer.input, 0))
+    for a in range(num_nodes):                            # path ends exchange their sums
+        for b in range(num_nodes):
+            if a != b:
+                chunk(rank(a, last), Buffer.input, 0).copy(rank(b, last), 'machines', a)
+    for b in range(num_nodes):
+        for a in range(num_nodes):
+            if a != b:
+                chunk(rank(b, last), Buffer.input, 0).reduce(chunk(rank(b, last), 'machines', a))
+    for node in range(num_nodes):                         # and back
+        for step in range(last - 1, -1, -1):
+            chunk(rank(node, step + 1), Buffer.input, 0).copy(rank(node, step), Buffer.input, 0)

@@ -81,7 +81,8 @@ def test_example_totals_and_execution(name, make_coll, body, instances, options,
                                          ('pipeline_allreduce.py', '4 2 --channels 2'),
                                          ('pipeline_allreduce.py', '3 1 --allpairs'),
                                          ('allreduce_binomial_tree.py', '6 2'), ('allreduce_2d.py', '3 3 2'),
-                                         ('allgather_two_pairs.py', '3')])
+                                         ('allgather_two_pairs.py', '3'), ('allreduce_dgx1_chain.py', '2 2'),
+                                         ('reduce_gather.py', '2 2 1')])
 def test_example_scripts_run(script, args):
     run = subprocess.run([sys.executable, os.path.join(ROOT, 'examples', 'mscclang', script)] + args.split() + ['--execute'],
                          capture_output=True, text=True)
