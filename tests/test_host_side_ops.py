@@ -186,3 +186,15 @@ def test_compiled_plan_tables_are_consistent():
     from msccl.language.ext_nvls import allreduce_nvls
     with pytest.raises(PlanError):
         compile_plan(load_xml(allreduce_nvls(4)), [0], slot)
+
+
+def test_setup_metadata_and_native_build_step():
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    run = subprocess.run([sys.executable, 'setup.py', '--name', '--version'], cwd=root, capture_output=True, text=True)
+    assert run.returncode == 0 and run.stdout.split() == ['msccl-b200', '0.1.0'], run.stderr
+    # the build step is the in-tree nvcc build; with an up-to-date module it only reports where it is
+    run = subprocess.run([sys.executable, 'setup.py', '-q', 'build_ext', '--inplace'], cwd=root, capture_output=True, text=True)
+    assert run.returncode == 0 and 'msccl: native module' in run.stdout, run.stdout + run.stderr
