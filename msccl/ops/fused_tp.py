@@ -3,6 +3,11 @@ each as ONE sm_100a kernel that overlaps NVLink traffic with tcgen05 tiles (``cs
 
 Sequence-parallel convention: activations enter and leave sharded by tokens
 (``[tokens_per_rank, hidden]`` per rank); weights are sharded along the FFN dimension.
+
+The chunk movement of both kernels is stated as MSCCLang programs in ``msccl.ops.schedules``
+(``all_gather_blocks``, ``reduce_scatter_blocks``: one chunk per 128-row block), where it is checked
+symbolically and run on the CPU interpreter; the kernels follow the same chunk order with the GEMM tiles in
+between.
 """
 import os
 

@@ -198,3 +198,22 @@ def test_setup_metadata_and_native_build_step():
     # the build step is the in-tree nvcc build; with an up-to-date module it only reports where it is
     run = subprocess.run([sys.executable, 'setup.py', '-q', 'build_ext', '--inplace'], cwd=root, capture_output=True, text=True)
     assert run.returncode == 0 and 'msccl: native module' in run.stdout, run.stdout + run.stderr
+
+
+@pytest.mark.parametrize('ranks,blocks', [(2, 3), (8, 8)])
+def test_fused_kernel_schedules_are_valid_programs(ranks, blocks):
+    # the chunk movement of the fused kernels, stated in the DSL: symbolic check, validator, interpreter
+    from msccl.interp import run_reference_check
+    from msccl.ops.schedules import all_gather_blocks, dispatch_blocks, reduce_scatter_blocks
+    from msccl.xml import load_xml, validate
+    for prog, coll in ((all_gather_blocks(ranks, blocks), 'allgather'), (reduce_scatter_blocks(ranks, blocks), 'reduce_scatter'),
+                       (dispatch_blocks(ranks), 'alltoall')):
+        algo = load_xml(prog.generate_xml())
+        assert algo.coll == coll and validate(algo) == []
+        assert run_reference_check(algo, 2, race_check=True) == 'pass (race-free)'
+    # reduce-scatter: every source visits the owners starting with its right neighbour (no two sources on one owner)
+    algo = load_xml(reduce_scatter_blocks(ranks, blocks).generate_xml())
+    for g in algo.gpus:
+        first_send = min((tb for tb in g.tbs if tb.send != -1 and tb.steps and tb.steps[0].type == 's'),
+                         key=lambda tb: tb.steps[0].srcoff, default=None)
+        assert first_send is not None
