@@ -21,8 +21,8 @@
 namespace py = pybind11;
 
 namespace msccl {
-cudaError_t launch_exec(const ExecArgs& args, int dtype, int proto, int grid, cudaStream_t stream, bool cooperative);
-int max_coresident_ctas(int dtype, int proto);
+cudaError_t launch_exec(const ExecArgs& args, int dtype, int proto, int width, int grid, cudaStream_t stream, bool cooperative);
+int max_coresident_ctas(int dtype, int proto, int width);
 cudaError_t launch_twoshot_allreduce(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int dtype,
                                      int rank, int nranks, SyncPage* const* syncs, unsigned long long timeout_ns, int ctas,
                                      cudaStream_t stream, void* rs_out);
@@ -92,26 +92,45 @@ void clear_status(uintptr_t sync_page) {
   check_rt(cudaMemset(&page->abort_flag, 0, sizeof(unsigned int) * 8), "cudaMemset(status)");
 }
 
-void launch(uintptr_t tbs, uintptr_t steps, uintptr_t ranks, long long chunk_elems, long long tile_elems,
-            long long slot_bytes, int iterations, int nranks, unsigned long long timeout_ns,
-            int first_tb, int grid, int dtype, int proto, uintptr_t stream, bool cooperative, bool bufs_from_args,
-            uintptr_t buf_in, uintptr_t buf_out, uintptr_t buf_scratch) {
+// One interpreter launch.  `geom` = [chunk_elems, tile_elems, slot_bytes, iterations, nranks, first_tb, grid, dtype, proto,
+// width]; `bufs` = [in, out, scratch] pointers of the launching rank (one rank per process; empty in emulation, where the
+// rank table carries them) and `elems` their sizes in elements; `peer_heaps` / `sym_off` / `direct_mask` describe which of
+// the buffers lie at the same offset of every rank's symmetric heap (stores straight into a peer's buffer); `trace` is 0
+// or a zeroed device array of grid x trace_steps x 4 words.
+void launch(uintptr_t tbs, uintptr_t steps, uintptr_t ranks, const std::vector<long long>& geom, unsigned long long timeout_ns,
+            uintptr_t stream, bool cooperative, const std::vector<uintptr_t>& bufs, const std::vector<long long>& elems,
+            const std::vector<uintptr_t>& peer_heaps, const std::vector<long long>& sym_off, int direct_mask,
+            unsigned long long epoch_base, uintptr_t trace, int trace_steps) {
+  if (geom.size() != 10) throw std::runtime_error("launch: geometry vector must have 10 entries");
+  if (!bufs.empty() && (bufs.size() != 3 || elems.size() != 3)) throw std::runtime_error("launch: three buffers and three sizes");
+  if (peer_heaps.size() > static_cast<size_t>(msccl::kMaxRanks) || (!sym_off.empty() && sym_off.size() != 3))
+    throw std::runtime_error("launch: bad peer table");
   msccl::ExecArgs a;
+  std::memset(&a, 0, sizeof(a));
   a.tbs = reinterpret_cast<const msccl::DevTb*>(tbs);
   a.steps = reinterpret_cast<const msccl::DevStep*>(steps);
   a.ranks = reinterpret_cast<const msccl::RankCtx*>(ranks);
-  a.chunk_elems = chunk_elems;
-  a.tile_elems = tile_elems;
-  a.slot_bytes = slot_bytes;
-  a.iterations = iterations;
-  a.nranks = nranks;
+  a.chunk_elems = geom[0];
+  a.tile_elems = geom[1];
+  a.slot_bytes = geom[2];
+  a.iterations = static_cast<int>(geom[3]);
+  a.nranks = static_cast<int>(geom[4]);
   a.timeout_ns = timeout_ns;
-  a.first_tb = first_tb;
-  a.bufs_from_args = bufs_from_args ? 1 : 0;
-  a.local_buf[0] = reinterpret_cast<void*>(buf_in);
-  a.local_buf[1] = reinterpret_cast<void*>(buf_out);
-  a.local_buf[2] = reinterpret_cast<void*>(buf_scratch);
-  check_rt(msccl::launch_exec(a, dtype, proto, grid, as_stream(stream), cooperative), "launch of the MSCCL-IR executor kernel");
+  a.first_tb = static_cast<int>(geom[5]);
+  a.bufs_from_args = bufs.empty() ? 0 : 1;
+  for (size_t b = 0; b < bufs.size(); ++b) {
+    a.local_buf[b] = reinterpret_cast<void*>(bufs[b]);
+    a.local_elems[b] = elems[b];
+  }
+  for (size_t r = 0; r < peer_heaps.size(); ++r) a.peer_heap[r] = reinterpret_cast<char*>(peer_heaps[r]);
+  for (int b = 0; b < 3; ++b) a.sym_off[b] = sym_off.empty() ? -1 : sym_off[b];
+  a.direct_mask = direct_mask;
+  a.epoch_base = epoch_base;
+  a.trace = reinterpret_cast<unsigned long long*>(trace);
+  a.trace_steps = trace_steps;
+  check_rt(msccl::launch_exec(a, static_cast<int>(geom[7]), static_cast<int>(geom[8]), static_cast<int>(geom[9]),
+                              static_cast<int>(geom[6]), as_stream(stream), cooperative),
+           "launch of the MSCCL-IR executor kernel");
 }
 
 py::dict layout() {
@@ -125,6 +144,8 @@ py::dict layout() {
   d["kMaxTbsPerRank"] = msccl::kMaxTbsPerRank;
   d["kFifoSlots"] = msccl::kFifoSlots;
   d["kExecThreads"] = msccl::kExecThreads;
+  d["kMaxBatch"] = msccl::kMaxBatch;
+  d["kMaxDirectCtas"] = msccl::kMaxDirectCtas;
   return d;
 }
 
@@ -176,7 +197,11 @@ PYBIND11_MODULE(_msccl_native, m) {
   m.def("download", &download);
   m.def("read_status", &read_status);
   m.def("clear_status", &clear_status);
-  m.def("launch", &launch, py::call_guard<py::gil_scoped_release>());
+  m.def("launch", &launch, py::arg("tbs"), py::arg("steps"), py::arg("ranks"), py::arg("geom"), py::arg("timeout_ns"),
+        py::arg("stream"), py::arg("cooperative"), py::arg("bufs") = std::vector<uintptr_t>(),
+        py::arg("elems") = std::vector<long long>(), py::arg("peer_heaps") = std::vector<uintptr_t>(),
+        py::arg("sym_off") = std::vector<long long>(), py::arg("direct_mask") = 0, py::arg("epoch_base") = 0ull,
+        py::arg("trace") = 0, py::arg("trace_steps") = 0);
   m.def("max_coresident_ctas", &msccl::max_coresident_ctas);
 
   m.def("vmm_granularity", &msccl::vmm_granularity);

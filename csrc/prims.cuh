@@ -86,4 +86,41 @@ template <> struct Vec16<__half> {
   }
 };
 
+
+// ---- element-wide accesses -----------------------------------------------------------------
+// Buffers whose chunks are not multiples of 16 bytes are moved one element per access: Wide<T, sizeof(T)>.
+// Wide<T, 16> is the 16-byte vector path.
+template <typename T, int W> struct Wide;
+
+template <typename T> struct Wide<T, 16> {
+  using V = uint4;
+  static __device__ __forceinline__ V add(V a, V b) { return Vec16<T>::add(a, b); }
+};
+template <> struct Wide<float, 4> {
+  using V = unsigned int;
+  static __device__ __forceinline__ V add(V a, V b) { return __float_as_uint(__uint_as_float(a) + __uint_as_float(b)); }
+};
+template <> struct Wide<__nv_bfloat16, 2> {
+  using V = unsigned short;
+  static __device__ __forceinline__ V add(V a, V b) {
+    const float s = __uint_as_float(static_cast<unsigned int>(a) << 16) + __uint_as_float(static_cast<unsigned int>(b) << 16);
+    return __bfloat16_as_ushort(__float2bfloat16_rn(s));
+  }
+};
+template <> struct Wide<__half, 2> {
+  using V = unsigned short;
+  static __device__ __forceinline__ V add(V a, V b) {
+    return __half_as_ushort(__float2half_rn(__half2float(__ushort_as_half(a)) + __half2float(__ushort_as_half(b))));
+  }
+};
+
+__device__ __forceinline__ uint2 ld_volatile_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_v2(uint2* p, uint2 v) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
 }  // namespace msccl

@@ -102,7 +102,7 @@ class Communicator:
         self._set_layout(world, ll_max_bytes, fifo_bytes, arena_bytes)
         for _ in range(world):
             ptr = self.native.device_malloc(self.heap_bytes, False)
-            self.native.device_memset(ptr, 0, self.off_fifo)
+            self.native.device_memset(ptr, 0, self.off_arena)      # flags and FIFOs (packets carry their flags)
             self.heap_ptrs.append(ptr)
             self._owned.append(('malloc', ptr))
         self._upload_tables()
@@ -191,7 +191,7 @@ class Communicator:
         self.heap_bytes = _align(self.heap_bytes, gran)
         mine = nat.vmm_create(self.device, self.heap_bytes, gran)
         self._owned.append(('vmm', mine))
-        nat.device_memset(mine['ptr'], 0, self.off_fifo)
+        nat.device_memset(mine['ptr'], 0, self.off_arena)          # flags and FIFOs (packets carry their flags)
         # descriptor exchange over abstract Unix sockets
         token = [uuid.uuid4().hex if self.rank == 0 else None]
         dist.broadcast_object_list(token, src=dist.get_global_rank(self.group, 0) if self.group else 0, group=self.group)
@@ -231,7 +231,7 @@ class Communicator:
         import torch.distributed as dist
         nat = self.native
         ptr = nat.device_malloc(self.heap_bytes, False)
-        nat.device_memset(ptr, 0, self.off_fifo)
+        nat.device_memset(ptr, 0, self.off_arena)                  # flags and FIFOs (packets carry their flags)
         self._owned.append(('malloc', ptr))
         handles = [None] * self.world
         dist.all_gather_object(handles, nat.ipc_export(ptr), group=self.group)
@@ -255,12 +255,15 @@ class Communicator:
         for p in (self.dev_heap_bases, self.dev_syncs, self.dev_staging, self.dev_rankctx):
             self._owned.append(('malloc', p))
 
-    def rankctx_bytes(self, buffers):
-        """``buffers[rank] = (in_ptr, out_ptr, scratch_ptr)`` for ranks this process runs."""
+    def rankctx_bytes(self, buffers, sizes=None):
+        """``buffers[rank] = (in_ptr, out_ptr, scratch_ptr)`` for ranks this process runs, ``sizes[rank]`` their
+        element counts (the bounds the kernel checks every step against)."""
         out = []
+        sizes = sizes or {}
         for r in range(self.world):
             b = buffers.get(r, (0, 0, 0))
-            out.append(_RANKCTX.pack(self.sync_ptr(r), self.fifo_ptr(r), b[0], b[1], b[2], 0, 0, 0))
+            n = sizes.get(r, (0, 0, 0))
+            out.append(_RANKCTX.pack(self.sync_ptr(r), self.fifo_ptr(r), b[0], b[1], b[2], n[0], n[1], n[2]))
         return b''.join(out)
 
     # -------------------------------------------------------- symmetric tensors
@@ -302,10 +305,12 @@ class Communicator:
                 raise ExecutorError(st, self.STATUS_NAMES.get(st[0], '?'))
 
     def reset_after_failure(self):
-        """Zero flags and counters of the local ranks (all ranks must do this together)."""
+        """Zero flags, counters, staging slots and FIFOs of the local ranks (all ranks must do this together).  The
+        FIFOs are part of it because the launch epoch restarts: a flag-in-data packet left by an earlier launch
+        must not carry a flag that a later launch expects."""
         torch.cuda.synchronize()
         for r in self.local_ranks:
-            self.native.device_memset(self.sync_ptr(r), 0, self.off_fifo)
+            self.native.device_memset(self.sync_ptr(r), 0, self.off_arena)
         if not self.emulated_mode:
             self.barrier()
 

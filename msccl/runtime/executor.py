@@ -24,7 +24,8 @@ import os
 import torch
 
 from msccl.runtime.comm import Communicator
-from msccl.runtime.plan import (HostPlan, PlanError, chunk_geometry, compile_plan, tile_geometry, K_FIFO_SLOTS)
+from msccl.runtime.plan import (HostPlan, PlanError, access_width, chunk_geometry, compile_plan, tile_geometry,
+                                K_FIFO_SLOTS)
 from msccl.xml.loader import AlgoIR, load_plan_table, load_xml
 
 DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
@@ -81,6 +82,8 @@ class Executor:
         self.cooperative = os.environ.get('MSCCL_EXEC_COOPERATIVE', '1') != '0'
         self.last_algorithm = None  # what the last collective call dispatched to
         self._ctx_cache = {}       # emulated mode: buffer pointers of all ranks -> device copy of the rank table
+        self.last_direct_mask = 0  # buffers (bit 0 input, 1 output, 2 scratch) the last run() stored into directly
+        self._trace = None
 
     # ------------------------------------------------------------------ plans
     def compile(self, algo_or_xml) -> DevicePlan:
@@ -109,10 +112,18 @@ class Executor:
         return None
 
     # ------------------------------------------------------------- interpreter
-    def run(self, plan: DevicePlan, inputs, outputs=None, stream=None):
+    def run(self, plan: DevicePlan, inputs, outputs=None, stream=None, direct='auto', trace=False, declared_elems=None):
         """Execute ``plan``.  ``inputs`` / ``outputs`` map every local rank to a contiguous CUDA
         tensor (a bare tensor is accepted when this process runs one rank).  For in-place
-        programs ``outputs`` may be omitted.  Returns the output tensors by rank."""
+        programs ``outputs`` may be omitted.  Returns the output tensors by rank.
+
+        ``direct``: sends whose matching receive is ``r`` / ``rcs`` store straight into the receiver's slot when the
+        receiving buffer is mapped on the sender - always in emulation; with one process per GPU when the tensor
+        (and, if the program receives into scratch, the plan's scratch) comes from ``Communicator.symmetric_empty``,
+        i.e. lies at the same heap offset on every rank.  ``'auto'`` decides per buffer, ``False`` forces the FIFO
+        path.  ``trace=True`` records per-step device time stamps, read back with ``last_trace()``.
+        ``declared_elems`` (rank -> (input, output, scratch) element counts) overrides the buffer sizes the kernel
+        checks every step against (a testing aid for the bounds check)."""
         comm, algo = self.comm, plan.algo
         if torch.is_tensor(inputs):
             inputs = {comm.local_ranks[0]: inputs}
@@ -131,20 +142,24 @@ class Executor:
             chunk = first.numel() // max(algo.gpus[comm.local_ranks[0]].o_chunks, 1)
         else:
             chunk = chunk_geometry(algo, comm.local_ranks[0], first.numel())
-        tile, iterations = tile_geometry(plan.host, chunk, esize, plan.slot_bytes)
-        buffers, results = {}, {}
+        if direct == 'auto':
+            direct = os.environ.get('MSCCL_DIRECT', '1') != '0'
+        buffers, sizes, results, tensors = {}, {}, {}, {}
         for r in comm.local_ranks:
             g = algo.gpus[r]
             t_in = inputs[r]
             assert t_in.is_cuda and t_in.is_contiguous() and t_in.dtype == dtype
             used = plan.host.extents[r]
             in_ptr, out_ptr = t_in.data_ptr(), 0
+            in_elems, out_elems = t_in.numel(), 0
+            out_t = None
             if algo.inplace and algo.coll == 'allgather':
                 # the caller's tensor is the gathered buffer; its own part is already in place
                 out_t = outputs.get(r, t_in)
                 if out_t.numel() != g.o_chunks * chunk:
                     raise PlanError(f'in-place all-gather needs the full {g.o_chunks * chunk}-element buffer')
                 in_ptr, out_ptr, results[r] = 0, out_t.data_ptr(), out_t
+                in_elems, out_elems = 0, out_t.numel()
             else:
                 if t_in.numel() < used['i'] * chunk:
                     raise PlanError(f'rank {r}: input of {t_in.numel()} elements, program reads {used["i"] * chunk}')
@@ -155,46 +170,102 @@ class Executor:
                     if out_t.numel() < used['o'] * chunk:
                         raise PlanError(f'rank {r}: output of {out_t.numel()} elements, program writes {used["o"] * chunk}')
                     out_ptr, results[r] = out_t.data_ptr(), out_t
+                    out_elems = out_t.numel()
                 else:
                     results[r] = t_in
-            scratch_ptr = 0
+            scratch_ptr, scratch_elems, scratch_t = 0, 0, None
             if used['s'] > 0:
                 need = used['s'] * chunk * esize
-                have = plan.scratch.get(r)
-                if have is None or have.numel() < need:
-                    have = torch.empty(need, dtype=torch.uint8, device=t_in.device)
-                    plan.scratch[r] = have
-                scratch_ptr = have.data_ptr()
-            for p in (in_ptr, out_ptr, scratch_ptr):
-                if p % 16 != 0:
-                    raise PlanError('buffers must be 16-byte aligned')
+                scratch_t = plan.scratch.get(r)
+                if scratch_t is None or scratch_t.numel() < need:
+                    scratch_t = self._new_scratch(plan, r, need, t_in.device, direct)
+                    plan.scratch[r] = scratch_t
+                scratch_ptr, scratch_elems = scratch_t.data_ptr(), scratch_t.numel() // esize
+            for ptr in (in_ptr, out_ptr, scratch_ptr):
+                if ptr % esize != 0:
+                    raise PlanError('buffers must be aligned to their element size')
             buffers[r] = (in_ptr, out_ptr, scratch_ptr)
+            sizes[r] = tuple(declared_elems[r]) if declared_elems else (in_elems, out_elems, scratch_elems)
+            tensors[r] = (None if in_ptr == 0 else t_in, out_t, scratch_t)
+        width = access_width(chunk, esize, [p for r in comm.local_ranks for p in buffers[r]])
+        proto = plan.host.proto
+        if proto == 2 and width != 16:
+            proto = 1                         # LL128 lines need 16-byte chunks; such calls run on the LL packets
+        tile, iterations = tile_geometry(plan.host, chunk, esize, plan.slot_bytes, width, proto)
         stream_h = (stream or torch.cuda.current_stream()).cuda_stream
         nat = comm.native
-        key = (DTYPE_CODES[dtype], plan.host.proto)
+        key = (DTYPE_CODES[dtype], proto, width)
         if key not in self._checked_grid:
             self._checked_grid[key] = nat.max_coresident_ctas(*key)
         if plan.grid > self._checked_grid[key]:
             raise PlanError(f'{plan.grid} threadblocks cannot be co-resident on this device '
                             f'(limit {self._checked_grid[key]})')
-        rankctx = comm.dev_rankctx
+        trace_ptr, trace_steps = 0, 0
+        if trace:
+            trace_steps = max(1, max(len(tb.steps) for g in algo.gpus for tb in g.tbs))
+            self._trace = torch.zeros(plan.grid * trace_steps * 4, dtype=torch.int64, device=first.device)
+            self._trace_shape = (plan, trace_steps)
+            trace_ptr = self._trace.data_ptr()
+        geom = [chunk, tile, plan.slot_bytes, iterations, comm.world, 0, plan.grid, key[0], proto, width]
         if comm.emulated_mode:
             # the per-rank buffer table lives on the device, one copy per distinct set of buffers: a
             # host-to-device copy per launch would queue behind any large input copy in flight
-            table = tuple(buffers[r] for r in comm.local_ranks)
+            table = tuple(buffers[r] + sizes[r] for r in comm.local_ranks)
             rankctx = self._ctx_cache.get(table)
             if rankctx is None:
                 if len(self._ctx_cache) >= 64:
                     nat.device_free(self._ctx_cache.pop(next(iter(self._ctx_cache))))
-                rankctx = self._ctx_cache[table] = nat.upload(comm.rankctx_bytes(buffers))
-            b = (0, 0, 0)
+                rankctx = self._ctx_cache[table] = nat.upload(comm.rankctx_bytes(buffers, sizes))
+            self.last_direct_mask = 7 if direct else 0
+            nat.launch(plan.dev_tbs, plan.dev_steps, rankctx, geom, comm.timeout_ns, stream_h, self.cooperative,
+                       direct_mask=self.last_direct_mask, trace=trace_ptr, trace_steps=trace_steps)
         else:
-            b = buffers[comm.rank]
-        nat.launch(plan.dev_tbs, plan.dev_steps, rankctx, chunk, tile, plan.slot_bytes, iterations,
-                   comm.world, comm.timeout_ns, 0, plan.grid, key[0], key[1], stream_h, self.cooperative,
-                   not comm.emulated_mode, b[0], b[1], b[2])
+            r = comm.rank
+            sym_off, mask = [-1, -1, -1], 0
+            if direct:
+                for b, t in enumerate(tensors[r]):
+                    off = comm.heap_offset_of(t) if t is not None else None
+                    if off is not None:
+                        sym_off[b], mask = off, mask | (1 << b)
+            self.last_direct_mask = mask
+            nat.launch(plan.dev_tbs, plan.dev_steps, comm.dev_rankctx, geom, comm.timeout_ns, stream_h, self.cooperative,
+                       bufs=list(buffers[r]), elems=list(sizes[r]), peer_heaps=list(comm.heap_ptrs), sym_off=sym_off,
+                       direct_mask=mask, trace=trace_ptr, trace_steps=trace_steps)
         self.launches += 1
         return results
+
+    def _new_scratch(self, plan, rank, nbytes, device, direct):
+        """Scratch of a plan: inside the symmetric arena when the program receives into scratch and the arena has
+        room (every rank allocates the same sizes in the same order, so the offsets agree), else ordinary memory."""
+        comm = self.comm
+        wants_symmetric = direct and not comm.emulated_mode and 's' in plan.host.direct_bufs.get(rank, ())
+        if wants_symmetric:
+            try:
+                return comm.symmetric_empty(nbytes, torch.uint8)[0]
+            except Exception:      # noqa: BLE001 - arena exhausted: the FIFO path needs no registered scratch
+                pass
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+    def last_trace(self):
+        """Step trace of the last ``run(..., trace=True)``: one dict per (rank, threadblock, step) with the first start
+        and last end (ns of the GPU's global timer, relative to the earliest start) and the total ns spent waiting
+        and moving data over all iterations."""
+        if getattr(self, '_trace', None) is None:
+            return []
+        plan, steps = self._trace_shape
+        raw = self._trace.cpu().view(-1, steps, 4)
+        starts = raw[:, :, 0][raw[:, :, 0] > 0]
+        origin = int(starts.min()) if starts.numel() else 0
+        rows, cta = [], 0
+        for r in self.comm.local_ranks:
+            for tb in plan.algo.gpus[r].tbs:
+                for si, st in enumerate(tb.steps):
+                    t0, t1, wait, move = (int(v) for v in raw[cta, si])
+                    if t1 or t0:
+                        rows.append({'rank': r, 'tb': tb.id, 'step': si, 'type': st.type, 'start_ns': t0 - origin,
+                                     'end_ns': t1 - origin, 'wait_ns': wait, 'move_ns': move})
+                cta += 1
+        return rows
 
     def _run_in_switch(self, plan, inputs, outputs, stream):
         """A program of in-switch steps (``msccl.language.ext_nvls``) on the native kernel of the same shape."""

@@ -52,12 +52,21 @@ def _cases():
     }
 
 
-def _run_both(algo, chunk_elems, dtype, fifo_bytes):
+def _run_both(algo, chunk_elems, dtype, fifo_bytes, direct='auto', misalign=0):
     from msccl.runtime import Communicator, Executor
     comm = Communicator.emulated(algo.ngpus, fifo_bytes=fifo_bytes)
     try:
         ex = Executor(comm)
         plan = ex.compile(algo)
+
+        def place(t):
+            """A device copy of ``t`` that starts ``misalign`` elements past a 16-byte boundary."""
+            if not misalign:
+                return t.cuda()
+            holder = torch.zeros(t.numel() + misalign, dtype=t.dtype, device='cuda')
+            holder[misalign:].copy_(t)
+            return holder[misalign:]
+
         gen = torch.Generator().manual_seed(42)
         host_in = [torch.randn(input_chunks_of(algo, r) * chunk_elems, generator=gen).to(dtype)
                    for r in range(algo.ngpus)]
@@ -65,15 +74,15 @@ def _run_both(algo, chunk_elems, dtype, fifo_bytes):
         dev_in, dev_out = {}, {}
         for r in range(algo.ngpus):
             if algo.inplace and algo.coll == 'allgather':
-                full = torch.zeros(algo.gpus[r].o_chunks * chunk_elems, dtype=dtype, device='cuda')
+                full = torch.zeros(algo.gpus[r].o_chunks * chunk_elems, dtype=dtype)
                 per = input_chunks_of(algo, r) * chunk_elems
-                full[r * per:(r + 1) * per] = host_in[r].cuda()
-                dev_in[r] = full
+                full[r * per:(r + 1) * per] = host_in[r]
+                dev_in[r] = place(full)
             else:
-                dev_in[r] = host_in[r].cuda()
+                dev_in[r] = place(host_in[r])
                 if algo.gpus[r].o_chunks > 0 and not algo.inplace:
-                    dev_out[r] = torch.zeros(algo.gpus[r].o_chunks * chunk_elems, dtype=dtype, device='cuda')
-        got = ex.run(plan, dev_in, dev_out)
+                    dev_out[r] = place(torch.zeros(algo.gpus[r].o_chunks * chunk_elems, dtype=dtype))
+        got = ex.run(plan, dev_in, dev_out, direct=direct)
         ex.check()
         assert ex.launches == 1
         for r in range(algo.ngpus):
@@ -102,6 +111,125 @@ def test_many_iterations_through_small_fifos(name):
     # 1 MiB of FIFO per rank forces tiles much smaller than a chunk: 40000-element chunks take
     # several iterations and the last tile is partial
     _run_both(_cases()[name](), 40000, torch.float32, 1 << 20)
+
+
+@pytest.mark.parametrize('name', ['ring8_simple', 'two_shot8_x2', 'alltoall8', 'allgather8_ring', 'reduce_scatter4',
+                                  'synth_allgather_nvswitch'])
+def test_fifo_only_path_matches_too(name):
+    # the same programs with stores into the receivers' buffers switched off: every tile takes the FIFO
+    _run_both(_cases()[name](), 4096, torch.float32, 8 << 20, direct=False)
+
+
+@pytest.mark.parametrize('name', ['ring4_ll128', 'ring8_ll128_x2', 'allgather8_ll128', 'allpairs4_ll128'])
+@pytest.mark.parametrize('dtype,chunk', [(torch.float32, 256), (torch.bfloat16, 40000), (torch.float16, 1000)])
+def test_ll128_lines(name, dtype, chunk):
+    # 128-byte lines with 120 bytes of payload: chunks that do not fill their last line, several iterations
+    cases = dict(_cases())
+    cases['ring8_ll128_x2'] = lambda: _program('ring', AllReduce(8, 8, True), lambda: allreduce_ring(8, 4), 2,
+                                               threadblock_policy=MANUAL, protocol='LL128')
+    cases['allgather8_ll128'] = lambda: _program('ag', AllGather(8, 1, False), lambda: allgather_direct(8), 1,
+                                                 protocol='LL128')
+    cases['allpairs4_ll128'] = lambda: _program('allpairs', AllReduce(4, 16, True), lambda: allreduce_allpairs(4), 1,
+                                                threadblock_policy=MANUAL, protocol='LL128')
+    _run_both(cases[name](), chunk, dtype, 1 << 20)
+
+
+@pytest.mark.parametrize('name', ['ring8_simple', 'ring8_ll_x2', 'ring4_ll128', 'two_shot8_x2', 'alltoall8',
+                                  'synth_allgather_nvswitch', 'allpairs4_ll_nop'])
+@pytest.mark.parametrize('dtype,chunk,misalign', [(torch.float16, 500, 0), (torch.bfloat16, 1001, 0), (torch.float32, 333, 0),
+                                                  (torch.float32, 256, 1), (torch.bfloat16, 4099, 3)])
+def test_chunks_that_are_not_multiples_of_16_bytes(name, dtype, chunk, misalign):
+    # 500 fp16 elements = 1000 bytes per chunk (a synthesised all-gather cut into 3 chunks meets such sizes), odd
+    # element counts, and buffers that do not start on a 16-byte boundary: element-wide accesses
+    _run_both(_cases()[name](), chunk, dtype, 2 << 20, misalign=misalign)
+
+
+def test_batched_reduces_match_separate_ones():
+    # all-pairs all-reduce: each rank adds the n - 1 received copies into its chunk; the runs of `re` steps are
+    # executed as one multi-input add and must round exactly like the separate passes of the CPU interpreter
+    for dtype in (torch.float32, torch.bfloat16):
+        for nop in (False, True):
+            algo = _program('allpairs', AllReduce(8, 64, True), lambda: allreduce_allpairs(8), 1,
+                            threadblock_policy=MANUAL, dependence_nop=nop)
+            from msccl.runtime.plan import compile_plan
+            assert compile_plan(algo, range(8), 64 << 10).batched_steps > 0
+            _run_both(algo, 2048, dtype, 8 << 20)
+
+
+def test_step_outside_the_declared_buffer_is_reported_not_executed():
+    """The kernel checks every step against the buffer sizes the host declared.  Here the declared sizes are
+    smaller than the tensors really are, so the "out-of-range" step still lies inside owned memory whatever the
+    check does; the launch must stop with the bounds status and leave the output untouched."""
+    from msccl.runtime import Communicator, Executor, ExecutorError
+    algo = _program('ag', AllGather(4, 1, False), lambda: allgather_direct(4))
+    comm = Communicator.emulated(4, fifo_bytes=1 << 20)
+    try:
+        comm.timeout_ns = int(1e9)        # the other ranks wait this long for the rank that stopped
+        ex = Executor(comm)
+        plan = ex.compile(algo)
+        ins = {r: torch.full((256,), float(r + 1), device='cuda') for r in range(4)}
+        outs = {r: torch.zeros(4 * 256, device='cuda') for r in range(4)}
+        # rank 2 declares an output of three chunks; the program writes four
+        declared = {r: (256, 4 * 256 if r != 2 else 3 * 256, 0) for r in range(4)}
+        ex.run(plan, ins, outs, declared_elems=declared)
+        with pytest.raises(ExecutorError):
+            ex.check()
+        status = comm.native.read_status(comm.sync_ptr(2))
+        assert status[0] == 6 and status[1] == 2          # STATUS_BOUNDS, reported by rank 2
+        assert torch.all(outs[2][3 * 256:] == 0)
+        comm.reset_after_failure()
+        comm.timeout_ns = int(20e9)
+        out = ex.run(plan, ins, outs)
+        ex.check()
+        assert torch.equal(out[2].view(4, 256)[:, 0].cpu(), torch.tensor([1.0, 2.0, 3.0, 4.0]))
+    finally:
+        comm.close()
+
+
+def test_step_trace_records_every_step():
+    from msccl.runtime import Communicator, Executor
+    algo = _cases()['ring8_simple']()
+    comm = Communicator.emulated(8, fifo_bytes=4 << 20)
+    try:
+        ex = Executor(comm)
+        plan = ex.compile(algo)
+        ins = {r: torch.ones(8 * 65536, device='cuda') for r in range(8)}
+        ex.run(plan, ins, trace=True)
+        ex.check()
+        rows = ex.last_trace()
+        assert len(rows) == algo.num_steps()
+        assert all(r['end_ns'] >= r['start_ns'] >= 0 and r['wait_ns'] >= 0 and r['move_ns'] >= 0 for r in rows)
+        assert any(r['move_ns'] > 0 for r in rows) and max(r['end_ns'] for r in rows) < 5e9
+        assert torch.all(ins[0] == 8.0)
+    finally:
+        comm.close()
+
+
+def test_direct_stores_were_taken_and_counters_survive_mixed_launches():
+    """Launches with and without direct stores alternate on one communicator: tile counters, opened-slot counters
+    and the mode bits in the tail words must stay consistent."""
+    from msccl.runtime import Communicator, Executor
+    ag = _cases()['allgather8_ring']()
+    ring = _cases()['ring8_simple']()
+    comm = Communicator.emulated(8, fifo_bytes=4 << 20)
+    try:
+        ex = Executor(comm)
+        p_ag, p_ring = ex.compile(ag), ex.compile(ring)
+        assert p_ag.host.direct_steps > 0 and p_ring.host.direct_steps > 0
+        for round_ in range(6):
+            direct = round_ % 3 != 1
+            ins = {r: torch.full((65536,), float(r + round_), device='cuda') for r in range(8)}
+            out = ex.run(p_ag, ins, direct=direct)
+            ex.check()
+            assert ex.last_direct_mask == (7 if direct else 0)
+            want = torch.arange(8, dtype=torch.float32) + round_
+            assert all(torch.equal(out[r].view(8, -1)[:, 5].cpu(), want) for r in range(8))
+            red = {r: torch.full((8 * 4096,), float(r + round_), device='cuda') for r in range(8)}
+            ex.run(p_ring, red, direct=not direct)
+            ex.check()
+            assert all(torch.all(red[r] == float(sum(range(8)) + 8 * round_)) for r in range(8))
+    finally:
+        comm.close()
 
 
 def test_repeated_launches_reuse_flags():
