@@ -37,6 +37,16 @@ def test_fused_moe_kernels():
     assert run.returncode == 0 and 'FUSED_MOE_OK' in run.stdout, run.stdout[-3000:] + run.stderr[-3000:]
 
 
+def test_pipeline_handover_and_gradient_buckets():
+    n = torch.cuda.device_count()
+    n = 4 if n >= 4 else 2
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={n}',
+           '--master-addr', '127.0.0.1', '--master-port', '29651', os.path.join(ROOT, 'tests', 'mp_parallel_worker.py')]
+    run = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0 and 'PIPELINE_GPU_OK' in run.stdout and 'GRADIENTS_GPU_OK' in run.stdout, \
+        run.stdout[-3000:] + run.stderr[-3000:]
+
+
 def test_rank_leaves_between_steps():
     # host-side failure detection on real ranks; NVLS off everywhere, plain peer loads/stores only
     n = torch.cuda.device_count()
