@@ -277,7 +277,7 @@ PYBIND11_MODULE(_msccl_native, m) {
   m.def("ag_gemm", [](uintptr_t x_local, uintptr_t b, uintptr_t d, int rows_per_rank, int N, int K, int ldb, int ldd, int rank,
                        int nranks, int comm_ctas, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs, size_t off_fused,
                        uintptr_t mc_base, size_t gathered_off, size_t gathered_bytes, uintptr_t error_words, int epilogue,
-                       int grid, int tuning, uintptr_t stream) {
+                       int grid, int tuning, uintptr_t order, uintptr_t stream) {
     msccl::sm100::AgGemmArgs g;
     std::memset(&g, 0, sizeof(g));
     g.x_local = reinterpret_cast<const void*>(x_local);
@@ -285,6 +285,7 @@ PYBIND11_MODULE(_msccl_native, m) {
     g.d = reinterpret_cast<void*>(d);
     g.rows_per_rank = rows_per_rank; g.N = N; g.K = K; g.ldb = ldb; g.ldd = ldd;
     g.rank = rank; g.nranks = nranks; g.comm_ctas = comm_ctas; g.tuning = tuning;
+    g.order = reinterpret_cast<const int*>(order);
     g.heap_bases = reinterpret_cast<char* const*>(heap_bases_dev);
     if (static_cast<int>(heap_ptrs.size()) != nranks || nranks > msccl::sm100::kFusedMaxRanks) throw std::runtime_error("bad rank count");
     for (int r = 0; r < nranks; ++r) {
@@ -300,7 +301,8 @@ PYBIND11_MODULE(_msccl_native, m) {
   // Fused GEMM -> reduce-scatter.
   m.def("gemm_rs", [](uintptr_t a, uintptr_t b, uintptr_t out, int rows_per_rank, int N, int K, int lda, int ldb, int rank,
                        int nranks, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs, size_t off_fused, size_t partial_off,
-                       uintptr_t error_words, int grid, uintptr_t stream) {
+                       uintptr_t error_words, int grid, uintptr_t order, uintptr_t reduce_order, int reduce_ctas,
+                       uintptr_t stream) {
     msccl::sm100::GemmRsArgs g;
     std::memset(&g, 0, sizeof(g));
     g.a = reinterpret_cast<const void*>(a);
@@ -313,6 +315,9 @@ PYBIND11_MODULE(_msccl_native, m) {
     for (int r = 0; r < nranks; ++r) g.pages[r] = reinterpret_cast<msccl::sm100::FusedPage*>(heap_ptrs[r] + off_fused);
     g.partial_off = partial_off;
     g.error_words = reinterpret_cast<int*>(error_words);
+    g.order = reinterpret_cast<const int*>(order);
+    g.reduce_order = reinterpret_cast<const int*>(reduce_order);
+    g.reduce_ctas = reduce_ctas;
     check_rt(msccl::sm100::launch_gemm_rs(g, grid, as_stream(stream)), "launch of the fused GEMM reduce-scatter kernel");
   });
   m.def("sm_count", &msccl::sm100::sm_count);

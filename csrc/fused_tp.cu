@@ -11,10 +11,12 @@
 //
 //   GEMM -> reduce-scatter   Y_owner[Ml, N] = sum over ranks of (H_r[n*Ml, K] * B_r[N, K]^T)[owner rows]
 //       The epilogue converts each accumulator tile to bf16 and stores it straight into the owner
-//       rank's partial buffer over NVLink, then bumps a per-(source, row block) counter on the
-//       owner.  Tiles are ordered owner-major starting at rank+1, so at any moment every rank sends
-//       to a different peer.  When its tiles are done every CTA turns into a reducer: it waits for
-//       the counters of a row block and sums the n partials in fp32, in rank order.
+//       rank's partial buffer over NVLink, then bumps the counter of its (source, row block) on the
+//       owner.  The row blocks are produced in the order of a table lowered from the schedule program
+//       (msccl.ops.schedules): block-major, so that block b of every owner is complete long before the
+//       GEMM ends.  A few CTAs at the end of the grid do no GEMM: they wait for the counters of one row
+//       block after the other and sum its n partials in fp32, in rank order, while the GEMM CTAs are
+//       still producing the later blocks.
 //
 // Buffers that peers write are double buffered by launch parity, so no barrier is needed between
 // consecutive calls (a rank can be at most one call ahead of a peer: it needs the peer's data of
@@ -32,6 +34,8 @@ namespace msccl {
 namespace sm100 {
 
 namespace {
+
+static_assert(sizeof(FusedPage) <= 64 * 1024, "the fused-kernel flag page must fit its 64 KiB slot of the heap");
 
 // Tile -> (column tile, row block).  Row blocks are numbered in arrival order (block-major over
 // sources).  Default: column tile fastest (CTAs running together share a row block of A).
@@ -149,7 +153,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
         for (int tile = cta; tile < num_tiles && ok; tile += gemm_ctas) {
           int tn, mb;
           ag_decode(tile, tiles_n, blocks_per_rank * g.nranks, g.tuning, tn, mb);
-          const int b = mb / g.nranks, src = (g.rank + mb % g.nranks) % g.nranks;
+          const int src = g.order[2 * mb], b = g.order[2 * mb + 1];
           const bool local = src == g.rank;
           if (!local) {
             if (!wait_flag_ge(&page->ag_flag[src][b], epoch, p.abort_flag)) {
@@ -187,7 +191,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
       for (int tile = cta; tile < num_tiles; tile += gemm_ctas) {
         int tn, mb;
         ag_decode(tile, tiles_n, blocks_per_rank * g.nranks, g.tuning, tn, mb);
-        const int b = mb / g.nranks, src = (g.rank + mb % g.nranks) % g.nranks;
+        const int src = g.order[2 * mb], b = g.order[2 * mb + 1];
         bool ok = mbar_wait(&p.acc_full[acc], acc_phase, p.abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -257,10 +261,49 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
 }
 
 // ============================================================ GEMM -> reduce-scatter
+// Sum of the n partial slabs of row block b (rows [b*BM, (b+1)*BM) of this rank's shard), in rank order,
+// fp32 accumulation, one rounding to bf16.  `part` of `parts` CTAs.
+__device__ __forceinline__ void reduce_row_block(const GemmRsArgs& g, const char* my_slabs, size_t slab_bytes, int b, int part,
+                                                 int parts) {
+  constexpr int RU = 4;          // vectors per thread per pass; with 8 sources that is 32 loads in flight
+  const size_t first = static_cast<size_t>(b) * BM * g.N * 2 / 16;
+  const size_t count = static_cast<size_t>(BM) * g.N * 2 / 16;
+  const size_t stride = static_cast<size_t>(parts) * blockDim.x;
+  char* out = static_cast<char*>(g.out);
+  for (size_t i = static_cast<size_t>(part) * blockDim.x + threadIdx.x; i < count; i += stride * RU) {
+    uint4 in[RU][kFusedMaxRanks];
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      const size_t ii = i + u * stride;
+#pragma unroll
+      for (int s = 0; s < kFusedMaxRanks; ++s)
+        if (s < g.nranks && ii < count) in[u][s] = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + (first + ii) * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < RU; ++u) {
+      const size_t ii = i + u * stride;
+      if (ii >= count) break;
+      float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+      for (int s = 0; s < kFusedMaxRanks; ++s) {
+        if (s < g.nranks) {
+          const uint32_t w[4] = {in[u][s].x, in[u][s].y, in[u][s].z, in[u][s].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc8[2 * e] += __uint_as_float(w[e] << 16);
+            acc8[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+          }
+        }
+      }
+      *reinterpret_cast<uint4*>(out + (first + ii) * 16) =
+          make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]), pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmRsArgs g) {
   extern __shared__ uint8_t smem_raw[];
-  const Pipe p = carve_smem<3>(smem_raw);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   FusedPage* page = g.pages[g.rank];
   if (g.error_words != nullptr && *reinterpret_cast<volatile int*>(g.error_words) != 0) return;   // an earlier launch gave up
@@ -270,173 +313,144 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int tiles_n = g.N / BN;
   const int num_tiles = blocks_per_rank * g.nranks * tiles_n;
   const int k_blocks = g.K / BK;
-  const int cta = blockIdx.x, ctas = gridDim.x;
-  const int my_tiles = (num_tiles - cta + ctas - 1) / ctas;
+  const int ctas = static_cast<int>(gridDim.x) - g.reduce_ctas;       // CTAs that run the GEMM
+  const int cta = blockIdx.x;
   // partial buffer on every rank: [parity][source rank][rows_per_rank][N] bf16
   const size_t slab_bytes = static_cast<size_t>(g.rows_per_rank) * g.N * 2;
   const size_t parity_off = g.partial_off + static_cast<size_t>(parity) * g.nranks * slab_bytes;
+  // Every source adds one count per (epilogue warp, tile) it stored: 4 * tiles_n per (source, row block) and
+  // launch.  The counters are never reset; rs_base remembers where the previous launch left them.
+  const unsigned long long per_block = 4ull * static_cast<unsigned long long>(tiles_n);
 
-  init_pipe<3>(p);
-  if (threadIdx.x == 0) {
-    prefetch_tensormap(&map_a);
-    prefetch_tensormap(&map_b);
-  }
-  if (warp == 1) tmem_alloc(p.tmem_slot, kTmemCols);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *p.tmem_slot;
+  if (cta >= ctas) {
+    // ------------------------------------------------------------------ reducer CTAs
+    __shared__ int s_ok;
+    const char* my_slabs = g.heap_bases[g.rank] + parity_off;
+    const int part = cta - ctas;
+    for (int i = 0; i < blocks_per_rank; ++i) {
+      const int b = g.reduce_order[i];
+      if (threadIdx.x == 0) s_ok = 1;
+      __syncthreads();
+      if (threadIdx.x < g.nranks) {
+        volatile int never = 0;
+        if (!wait_flag_ge(&page->rs_count[threadIdx.x][b], page->rs_base[threadIdx.x][b] + per_block, &never)) {
+          if (g.error_words != nullptr && atomicCAS(&g.error_words[0], 0, static_cast<int>(GEMM_TIMEOUT_FLAG)) == 0) {
+            g.error_words[1] = blockIdx.x;
+            g.error_words[2] = 3;
+            g.error_words[3] = threadIdx.x * 64 + b;
+          }
+          s_ok = 0;
+        }
+      }
+      __syncthreads();
+      if (s_ok == 0) break;
+      reduce_row_block(g, my_slabs, slab_bytes, b, part, g.reduce_ctas);
+    }
+  } else {
+    // ------------------------------------------------------------------ GEMM CTAs
+    const Pipe p = carve_smem<3>(smem_raw);
+    const int my_tiles = (num_tiles - cta + ctas - 1) / ctas;
+    init_pipe<3>(p);
+    if (threadIdx.x == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+    }
+    if (warp == 1) tmem_alloc(p.tmem_slot, kTmemCols);
+    tc_fence_before_sync();
+    asm volatile("bar.sync 1, %0;" ::"r"(kGemmThreads) : "memory");
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *p.tmem_slot;
 
-  // tile order: owner-major starting with rank+1 (own rows last), then row block, then column tile
-  auto decode = [&](int tile, int& owner, int& b, int& tn) {
-    tn = tile % tiles_n;
-    const int mb = tile / tiles_n;
-    b = mb % blocks_per_rank;
-    owner = (g.rank + 1 + mb / blocks_per_rank) % g.nranks;
-  };
+    // tile -> (owner, row block of the owner's shard, column tile): row blocks in the order of the table
+    auto decode = [&](int tile, int& owner, int& b, int& tn) {
+      tn = tile % tiles_n;
+      const int rb = tile / tiles_n;
+      owner = g.order[2 * rb];
+      b = g.order[2 * rb + 1];
+    };
 
-  if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = cta; tile < num_tiles && ok; tile += ctas) {
+    if (warp == 0) {
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = cta; tile < num_tiles && ok; tile += ctas) {
+          int owner, b, tn;
+          decode(tile, owner, b, tn);
+          const int a_row = owner * g.rows_per_rank + b * BM;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(&p.empty_bar[stage], phase ^ 1, p.abort_flag)) {
+              gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_EMPTY, 0, stage);
+              ok = false;
+              break;
+            }
+            uint8_t* a_dst = p.stage_base + static_cast<size_t>(stage) * kStageBytes;
+            mbar_expect_tx(&p.full_bar[stage], kStageBytes);
+            tma_load_2d(a_dst, &map_a, &p.full_bar[stage], kb * BK, a_row);
+            tma_load_2d(a_dst + kABytes, &map_b, &p.full_bar[stage], kb * BK, tn * BN);
+            if (++stage == 3) { stage = 0; phase ^= 1; }
+          }
+        }
+        if (!ok) drain_loads<3>(p);
+      }
+    } else if (warp == 1) {
+      if (lane == 0) mma_role<3>(p, tmem_base, my_tiles, k_blocks, g.error_words);
+    } else {
+      const int quarter = warp % 4;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int tile = cta; tile < num_tiles; tile += ctas) {
         int owner, b, tn;
         decode(tile, owner, b, tn);
-        const int a_row = owner * g.rows_per_rank + b * BM;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&p.empty_bar[stage], phase ^ 1, p.abort_flag)) {
-            gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_EMPTY, 0, stage);
-            ok = false;
-            break;
-          }
-          uint8_t* a_dst = p.stage_base + static_cast<size_t>(stage) * kStageBytes;
-          mbar_expect_tx(&p.full_bar[stage], kStageBytes);
-          tma_load_2d(a_dst, &map_a, &p.full_bar[stage], kb * BK, a_row);
-          tma_load_2d(a_dst + kABytes, &map_b, &p.full_bar[stage], kb * BK, tn * BN);
-          if (++stage == 3) { stage = 0; phase ^= 1; }
+        bool ok = mbar_wait(&p.acc_full[acc], acc_phase, p.abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_ACC, 2, acc);
+          break;
         }
-      }
-      if (!ok) drain_loads<3>(p);
-    }
-  } else if (warp == 1) {
-    if (lane == 0) mma_role<3>(p, tmem_base, my_tiles, k_blocks, g.error_words);
-  } else {
-    const int quarter = warp % 4;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    int cur_owner = -1, tiles_for_owner = 0;
-    for (int tile = cta; tile < num_tiles; tile += ctas) {
-      int owner, b, tn;
-      decode(tile, owner, b, tn);
-      bool ok = mbar_wait(&p.acc_full[acc], acc_phase, p.abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) {
-        if (lane == 0) gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_ACC, 2, acc);
-        break;
-      }
-      tc_fence_after_sync();
-      // destination: owner's slab for source = me, local row inside the owner's shard
-      if (owner != cur_owner) {
-        // all tiles of the previous owner are stored: make them visible there, then count them
-        if (cur_owner >= 0 && lane == 0) {
-          __threadfence_system();
-          red_add_release_sys(&g.pages[cur_owner]->rs_count[g.rank][0], static_cast<unsigned long long>(tiles_for_owner));
-        }
-        cur_owner = owner;
-        tiles_for_owner = 0;
-      }
-      char* slab = g.heap_bases[owner] + parity_off + static_cast<size_t>(g.rank) * slab_bytes;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      uint8_t* stage_warp = p.staging + (warp - 2) * kStagingPerWarp;
-      stage_quarter_bf16(taddr, stage_warp, lane, 1.0f);
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p.acc_empty[acc]);      // accumulator is free as soon as it sits in shared memory
-      // one row (512 contiguous bytes) per store instruction, 8 rows in flight
-      char* dst0 = slab + ((static_cast<size_t>(b) * BM + quarter * 32) * g.N + static_cast<size_t>(tn) * BN) * 2 + lane * 16;
+        tc_fence_after_sync();
+        // destination: the owner's slab for source = me, local row inside the owner's shard
+        char* slab = g.heap_bases[owner] + parity_off + static_cast<size_t>(g.rank) * slab_bytes;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+        uint8_t* stage_warp = p.staging + (warp - 2) * kStagingPerWarp;
+        stage_quarter_bf16(taddr, stage_warp, lane, 1.0f);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p.acc_empty[acc]);      // accumulator is free as soon as it sits in shared memory
+        // one row (512 contiguous bytes) per store instruction, 8 rows in flight
+        char* dst0 = slab + ((static_cast<size_t>(b) * BM + quarter * 32) * g.N + static_cast<size_t>(tn) * BN) * 2 + lane * 16;
 #pragma unroll 1
-      for (int r0 = 0; r0 < 32; r0 += 8) {
-        uint4 d[8];
+        for (int r0 = 0; r0 < 32; r0 += 8) {
+          uint4 d[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) d[u] = *reinterpret_cast<const uint4*>(stage_warp + (r0 + u) * kStagePitch + lane * 16);
+          for (int u = 0; u < 8; ++u) d[u] = *reinterpret_cast<const uint4*>(stage_warp + (r0 + u) * kStagePitch + lane * 16);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) *reinterpret_cast<uint4*>(dst0 + static_cast<size_t>(r0 + u) * g.N * 2) = d[u];
+          for (int u = 0; u < 8; ++u) *reinterpret_cast<uint4*>(dst0 + static_cast<size_t>(r0 + u) * g.N * 2) = d[u];
+        }
+        __syncwarp();
+        // this quarter of the tile is on its way: make it visible on the owner, then count it there
+        if (lane == 0) {
+          __threadfence_system();
+          red_add_release_sys(&g.pages[owner]->rs_count[g.rank][b], 1ull);
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
-      __syncwarp();
-      ++tiles_for_owner;
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
-    if (cur_owner >= 0 && lane == 0) {
-      __threadfence_system();
-      red_add_release_sys(&g.pages[cur_owner]->rs_count[g.rank][0], static_cast<unsigned long long>(tiles_for_owner));
+    tc_fence_before_sync();
+    asm volatile("bar.sync 1, %0;" ::"r"(kGemmThreads) : "memory");
+    if (warp == 1) {
+      tc_fence_after_sync();
+      tmem_dealloc(tmem_base, kTmemCols);
     }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
   }
 
-  // ------------------------------------------------------------------ reduction of my rows
-  // work item = (row block b, 16-byte column vector group); every CTA takes a strided share
-  // Every source adds one count per (epilogue warp, tile) it stored into my slab: 4 * tiles_n *
-  // blocks_per_rank per launch.  The counters are never reset; rs_base remembers where the
-  // previous launch left them.
-  const unsigned long long per_launch = 4ull * static_cast<unsigned long long>(tiles_n) * blocks_per_rank;
-  const char* my_slabs = g.heap_bases[g.rank] + parity_off;
-  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(g.out);
-  const size_t total_vecs = static_cast<size_t>(g.rows_per_rank) * g.N * 2 / 16;
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) {
-    int ok = 1;
-    for (int s = 0; s < g.nranks && ok; ++s)
-      if (!wait_flag_ge(&page->rs_count[s][0], page->rs_base[s][0] + per_launch, p.abort_flag)) {
-        gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_FLAG, 3, s);
-        ok = 0;
-      }
-    s_ok = ok;
-  }
-  __syncthreads();
-  if (s_ok != 0) {
-    constexpr int RU = 4;          // vectors per thread per pass; with 8 sources that is 32 loads in flight
-    const size_t stride = static_cast<size_t>(ctas) * blockDim.x;
-    for (size_t v = static_cast<size_t>(cta) * blockDim.x + threadIdx.x; v < total_vecs; v += stride * RU) {
-      uint4 part[RU][kFusedMaxRanks];
-#pragma unroll
-      for (int u = 0; u < RU; ++u) {
-        const size_t vv = v + u * stride;
-#pragma unroll
-        for (int s = 0; s < kFusedMaxRanks; ++s)
-          if (s < g.nranks && vv < total_vecs) part[u][s] = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + vv * 16);
-      }
-#pragma unroll
-      for (int u = 0; u < RU; ++u) {
-        const size_t vv = v + u * stride;
-        if (vv >= total_vecs) break;
-        float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-        for (int s = 0; s < kFusedMaxRanks; ++s) {
-          if (s < g.nranks) {
-            const uint32_t w[4] = {part[u][s].x, part[u][s].y, part[u][s].z, part[u][s].w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              acc8[2 * e] += __uint_as_float(w[e] << 16);
-              acc8[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-            }
-          }
-        }
-        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + vv * 16) =
-            make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]), pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
-      }
-    }
-  }
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(&page->rs_done, 1u) == gridDim.x - 1u) {
-      for (int s = 0; s < g.nranks; ++s) page->rs_base[s][0] += per_launch;
+      // every CTA of this rank is through: the reducers have seen all counters of this launch
+      for (int s = 0; s < g.nranks; ++s)
+        for (int b = 0; b < blocks_per_rank; ++b) page->rs_base[s][b] += per_block;
       page->rs_done = 0;
       page->rs_epoch = epoch;
     }
@@ -447,7 +461,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 cudaError_t launch_ag_gemm(const AgGemmArgs& g, int epilogue, int grid, cudaStream_t stream) {
   if (g.K % BK != 0 || g.N % BN != 0 || g.rows_per_rank % BM != 0 || g.rows_per_rank / BM > kFusedMaxBlocks ||
-      g.nranks > kFusedMaxRanks || g.comm_ctas < 1 || grid <= g.comm_ctas)
+      g.nranks > kFusedMaxRanks || g.comm_ctas < 1 || grid <= g.comm_ctas || g.order == nullptr)
     return cudaErrorInvalidValue;
   const uint64_t all_rows = static_cast<uint64_t>(g.rows_per_rank) * g.nranks;
   CUtensorMap map_local = make_bf16_kmajor_map(g.x_local, g.rows_per_rank, g.K, g.K, BM);
@@ -471,7 +485,8 @@ cudaError_t launch_ag_gemm(const AgGemmArgs& g, int epilogue, int grid, cudaStre
 
 cudaError_t launch_gemm_rs(const GemmRsArgs& g, int grid, cudaStream_t stream) {
   if (g.K % BK != 0 || g.N % BN != 0 || g.rows_per_rank % BM != 0 || g.rows_per_rank / BM > kFusedMaxBlocks ||
-      g.nranks > kFusedMaxRanks || grid < 1)
+      g.nranks > kFusedMaxRanks || g.reduce_ctas < 1 || grid <= g.reduce_ctas || g.order == nullptr ||
+      g.reduce_order == nullptr)
     return cudaErrorInvalidValue;
   CUtensorMap map_a = make_bf16_kmajor_map(g.a, static_cast<uint64_t>(g.rows_per_rank) * g.nranks, g.K, g.lda, BM);
   CUtensorMap map_b = make_bf16_kmajor_map(g.b, g.N, g.K, g.ldb, BN);

@@ -20,6 +20,8 @@ struct alignas(128) FusedPage {
   unsigned int ag_done, rs_done;                                   // local: CTAs of the running launch that finished
   // MoE dispatch / combine
   unsigned long long moe_flag[kFusedMaxRanks][4];
+  unsigned long long moe_count[kFusedMaxRanks];                    // [source] += 1 per combine row group stored
+  unsigned long long moe_base[kFusedMaxRanks];                     // local: moe_count at the end of the previous launch
   unsigned long long moe_epoch;
   unsigned int moe_done, moe_pad;
 };
@@ -31,6 +33,8 @@ struct AgGemmArgs {
   int rows_per_rank, N, K, ldb, ldd;
   int rank, nranks, comm_ctas;
   int tuning;                     // bit 0: order tiles row-block-fastest inside a (block, source) wave group
+  const int* order;               // device array of nranks * blocks (source rank, block) pairs: the row blocks in the order
+                                  // the GEMM tiles consume them, as lowered from the schedule program
   char* const* heap_bases;        // device array: every rank's heap as mapped here
   char* heap_bases_host[kFusedMaxRanks];
   FusedPage* pages[kFusedMaxRanks];
@@ -50,6 +54,10 @@ struct GemmRsArgs {
   FusedPage* pages[kFusedMaxRanks];
   size_t partial_off;             // offset of the partial buffer [2][nranks][rows_per_rank, N] in every heap
   int* error_words;
+  const int* order;               // device array of nranks * blocks (owner rank, block) pairs: the row blocks in the order
+                                  // the GEMM tiles produce them, as lowered from the schedule program
+  const int* reduce_order;        // device array of blocks: this rank's row blocks in the order they become complete
+  int reduce_ctas;                // CTAs (the last ones of the grid) that only reduce
 };
 
 cudaError_t launch_ag_gemm(const AgGemmArgs& args, int epilogue, int grid, cudaStream_t stream);

@@ -410,7 +410,7 @@ moe_gemm_combine_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     __syncwarp();
     if (lane < g.nranks) {
       __threadfence_system();
-      red_add_release_sys(&g.pages[lane]->rs_count[g.rank][1], 1ull);
+      red_add_release_sys(&g.pages[lane]->moe_count[g.rank], 1ull);
     }
   }
   tc_fence_before_sync();
@@ -426,7 +426,7 @@ moe_gemm_combine_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   if (threadIdx.x == 0) {
     int ok = 1;
     for (int s = 0; s < g.nranks && ok; ++s)
-      if (!wait_flag_ge(&page->rs_count[s][1], page->rs_base[s][1] + per_launch, p.abort_flag)) {
+      if (!wait_flag_ge(&page->moe_count[s], page->moe_base[s] + per_launch, p.abort_flag)) {
         gemm_fail(g.error_words, p.abort_flag, GEMM_TIMEOUT_FLAG, 3, s);
         ok = 0;
       }
@@ -457,7 +457,7 @@ moe_gemm_combine_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   if (threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(&page->moe_done, 1u) == gridDim.x - 1u) {
-      for (int s = 0; s < g.nranks; ++s) page->rs_base[s][1] += per_launch;
+      for (int s = 0; s < g.nranks; ++s) page->moe_base[s] += per_launch;
       page->moe_done = 0;
       page->moe_pad = 0;
       page->moe_epoch = epoch;

@@ -6,8 +6,9 @@ Sequence-parallel convention: activations enter and leave sharded by tokens
 
 The chunk movement of both kernels is stated as MSCCLang programs in ``msccl.ops.schedules``
 (``all_gather_blocks``, ``reduce_scatter_blocks``: one chunk per 128-row block), where it is checked
-symbolically and run on the CPU interpreter; the kernels follow the same chunk order with the GEMM tiles in
-between.
+symbolically and run on the CPU interpreter.  The compiled programs are lowered into row-block order tables
+(``msccl.ops.schedules.fused_tp_tables``) which the kernels take as arguments: the GEMM tiles walk the row
+blocks in that order.
 """
 import os
 
@@ -20,7 +21,7 @@ from msccl.runtime.comm import Communicator
 class FusedTensorParallel:
     """Holds the symmetric buffers of the two fused kernels for fixed shapes."""
 
-    def __init__(self, comm: Communicator, tokens_per_rank: int, hidden: int, comm_ctas: int = 16):
+    def __init__(self, comm: Communicator, tokens_per_rank: int, hidden: int, comm_ctas: int = 8):
         if comm.emulated_mode:
             raise ValueError('the fused kernels need one process per GPU')
         if tokens_per_rank % 128 or hidden % 256:
@@ -38,6 +39,18 @@ class FusedTensorParallel:
         self.launches = 0
         self.tuning = int(os.environ.get('MSCCL_AG_TUNING', '0'))
         self.grid = int(os.environ.get('MSCCL_AG_GRID', '0'))
+        self.reduce_ctas = int(os.environ.get('MSCCL_RS_REDUCE_CTAS', '12'))
+        self.set_schedule()
+
+    def set_schedule(self, ag_channels=1, rs_channels=1):
+        """Install the row-block order tables lowered from the schedule programs (``msccl.ops.schedules``); the
+        channel counts select among the programs: with c channels a round of the lowering holds c blocks per peer."""
+        from msccl.ops.schedules import fused_tp_tables
+        ag, rs, red = fused_tp_tables(self.n, self.rows // 128, self.comm.rank, ag_channels, rs_channels)
+        dev = f'cuda:{self.comm.device}'
+        self.ag_order = torch.tensor(ag, dtype=torch.int32, device=dev)
+        self.rs_order = torch.tensor(rs, dtype=torch.int32, device=dev)
+        self.reduce_order = torch.tensor(red, dtype=torch.int32, device=dev)
 
     def all_gather_gemm(self, x_local, weight, epilogue='none', out=None, stream=None):
         """``epilogue(gather(x_local) @ weight.T)``: x_local [rows, hidden], weight [N, hidden] -> [n*rows, N (or N/2)]."""
@@ -53,7 +66,7 @@ class FusedTensorParallel:
         c.native.ag_gemm(x_local.data_ptr(), weight.data_ptr(), out.data_ptr(), self.rows, n_out, k, weight.stride(0),
                          out.stride(0), c.rank, self.n, self.comm_ctas, c.dev_heap_bases, list(c.heap_ptrs), c.off_fused,
                          c.mc_base, self.gathered_off, self.gathered_bytes, _errors(x_local.device).data_ptr(),
-                         1 if swiglu else 0, self.grid or self.sms, self.tuning, stream_h)
+                         1 if swiglu else 0, self.grid or self.sms, self.tuning, self.ag_order.data_ptr(), stream_h)
         self.launches += 1
         return out
 
@@ -69,6 +82,7 @@ class FusedTensorParallel:
         stream_h = (stream or torch.cuda.current_stream()).cuda_stream
         c.native.gemm_rs(a.data_ptr(), weight.data_ptr(), out.data_ptr(), self.rows, self.hidden, k, a.stride(0),
                          weight.stride(0), c.rank, self.n, c.dev_heap_bases, list(c.heap_ptrs), c.off_fused, self.partial_off,
-                         _errors(a.device).data_ptr(), self.sms, stream_h)
+                         _errors(a.device).data_ptr(), self.sms, self.rs_order.data_ptr(), self.reduce_order.data_ptr(),
+                         min(self.reduce_ctas, self.sms - 1), stream_h)
         self.launches += 1
         return out

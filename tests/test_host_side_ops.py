@@ -217,3 +217,34 @@ def test_fused_kernel_schedules_are_valid_programs(ranks, blocks):
         first_send = min((tb for tb in g.tbs if tb.send != -1 and tb.steps and tb.steps[0].type == 's'),
                          key=lambda tb: tb.steps[0].srcoff, default=None)
         assert first_send is not None
+
+
+def test_fused_kernel_order_tables_are_lowered_from_the_programs():
+    # the tables the fused kernels take as arguments come out of the compiled schedule programs: every row block
+    # exactly once, own blocks first for the all-gather, block-major production for the reduce-scatter, and a
+    # different program (blocks spread over two channels) gives different tables
+    from msccl.ops.schedules import (all_gather_blocks, fused_tp_tables, lower_all_gather, lower_reduce_scatter,
+                                     reduce_scatter_blocks)
+    from msccl.xml import load_xml
+    pairs = lambda flat: [(flat[i], flat[i + 1]) for i in range(0, len(flat), 2)]       # noqa: E731
+    n, blocks, rank = 8, 8, 3
+    ag, rs, red = fused_tp_tables(n, blocks, rank)
+    ag, rs = pairs(ag), pairs(rs)
+    everything = sorted((r, b) for r in range(n) for b in range(blocks))
+    assert sorted(ag) == everything and sorted(rs) == everything and sorted(red) == list(range(blocks))
+    assert ag[:blocks] == [(rank, b) for b in range(blocks)]                 # local blocks need no flag: they lead
+    assert [b for _, b in ag[blocks:]] == sorted(b for _, b in ag[blocks:])   # then block 0 of every source, block 1, ...
+    assert [b for _, b in rs] == sorted(b for _, b in rs)                     # block 0 for every owner, then block 1, ...
+    for b in range(blocks):                                                   # own block last among the block's owners
+        assert [o for o, bb in rs if bb == b][-1] == rank
+    assert red == list(range(blocks))
+    # straight from the MSCCL-IR, another program -> another order
+    one = lower_reduce_scatter(load_xml(reduce_scatter_blocks(4, 4, channels=1).generate_xml()), 1)[0]
+    two = lower_reduce_scatter(load_xml(reduce_scatter_blocks(4, 4, channels=2).generate_xml()), 1)[0]
+    assert sorted(one) == sorted(two) and one != two
+    assert [b for _, b in two][:4] == [0, 1, 0, 1]                            # a round now holds two blocks per owner
+    g1 = lower_all_gather(load_xml(all_gather_blocks(4, 4, channels=1).generate_xml()), 2)
+    g2 = lower_all_gather(load_xml(all_gather_blocks(4, 4, channels=2).generate_xml()), 2)
+    assert g1 != g2 and g1[:4] == g2[:4] == [(2, b) for b in range(4)]
+    # one rank: nothing moves
+    assert fused_tp_tables(1, 4, 0) == ([0, 0, 0, 1, 0, 2, 0, 3], [0, 0, 0, 1, 0, 2, 0, 3], [0, 1, 2, 3])
