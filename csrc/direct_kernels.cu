@@ -20,6 +20,8 @@
 // All waits are bounded; on expiry the kernel writes a status code to the rank's sync page and
 // returns.  These are the hand-tuned counterparts of the allreduce_one_shot / allreduce_two_shot
 // MSCCLang programs (msccl/programs/allreduce.py), selected by the plan dispatcher by size.
+#include <tuple>
+
 #include "msccl_device.h"
 #include "prims.cuh"
 
@@ -344,17 +346,27 @@ oneshot_ll_kernel(const void* in, void* out, char* const* staging, long long byt
   }
 }
 
+// The CTAs of these kernels wait on the same-numbered CTA of every other rank (rank_barrier) or on packets any
+// CTA of a peer may write, so all CTAs of a launch must be resident together - also when the GPU is shared with a
+// GEMM on another stream.  A cooperative launch guarantees that (and fails instead of deadlocking when the grid
+// cannot fit).
+template <typename... Params, typename... Args>
+cudaError_t launch_coresident(void (*kernel)(Params...), int ctas, cudaStream_t stream, Args... args) {
+  std::tuple<Params...> values{static_cast<Params>(args)...};
+  void* ptrs[sizeof...(Params)];
+  std::apply([&](auto&... v) { int i = 0; ((ptrs[i++] = static_cast<void*>(&v)), ...); }, values);
+  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(ctas), dim3(kDirectThreads), ptrs, 0, stream);
+}
+
 template <typename T>
 cudaError_t twoshot_typed(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int rank, int nranks,
                           SyncPage* const* syncs, unsigned long long timeout_ns, int ctas, cudaStream_t stream, char* rs_out) {
   if (mc_base != nullptr) {
-    twoshot_allreduce_kernel<T, true><<<ctas, kDirectThreads, 0, stream>>>(heap_bases, mc_base + offset, offset, bytes, rank,
-                                                                         nranks, syncs, timeout_ns, rs_out);
-  } else {
-    twoshot_allreduce_kernel<T, false><<<ctas, kDirectThreads, 0, stream>>>(heap_bases, nullptr, offset, bytes, rank, nranks,
-                                                                          syncs, timeout_ns, rs_out);
+    return launch_coresident(twoshot_allreduce_kernel<T, true>, ctas, stream, heap_bases, mc_base + offset, offset, bytes, rank,
+                             nranks, syncs, timeout_ns, rs_out);
   }
-  return cudaGetLastError();
+  return launch_coresident(twoshot_allreduce_kernel<T, false>, ctas, stream, heap_bases, static_cast<char*>(nullptr), offset, bytes,
+                           rank, nranks, syncs, timeout_ns, rs_out);
 }
 
 // mode: 0 all-reduce, 1 all-gather, 2 reduce-scatter, 3 all-to-all
@@ -362,13 +374,12 @@ template <typename T>
 cudaError_t oneshot_typed(const void* in, void* out, char* const* staging, long long bytes, long long slot_bytes, int rank,
                           int nranks, SyncPage* sync, unsigned long long timeout_ns, int ctas, int mode, cudaStream_t stream) {
   switch (mode) {
-    case 0: oneshot_ll_kernel<T, false, true><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns); break;
-    case 1: oneshot_ll_kernel<T, false, false><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns); break;
-    case 2: oneshot_ll_kernel<T, true, true><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns); break;
-    case 3: oneshot_ll_kernel<T, true, false><<<ctas, kDirectThreads, 0, stream>>>(in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns); break;
+    case 0: return launch_coresident(oneshot_ll_kernel<T, false, true>, ctas, stream, in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns);
+    case 1: return launch_coresident(oneshot_ll_kernel<T, false, false>, ctas, stream, in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns);
+    case 2: return launch_coresident(oneshot_ll_kernel<T, true, true>, ctas, stream, in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns);
+    case 3: return launch_coresident(oneshot_ll_kernel<T, true, false>, ctas, stream, in, out, staging, bytes, slot_bytes, rank, nranks, sync, timeout_ns);
     default: return cudaErrorInvalidValue;
   }
-  return cudaGetLastError();
 }
 
 }  // namespace
@@ -395,14 +406,10 @@ cudaError_t launch_push(const void* src, bool same_src, char* const* heap_bases,
       ctas > kMaxDirectCtas || nranks > kMaxRanks)
     return cudaErrorInvalidValue;
   const char* s = static_cast<const char*>(src);
-  if (!same_src) {
-    push_kernel<false, false><<<ctas, kDirectThreads, 0, stream>>>(s, heap_bases, nullptr, dst_offset, block_bytes, rank, nranks, syncs, timeout_ns);
-  } else if (mc_base != nullptr) {
-    push_kernel<true, true><<<ctas, kDirectThreads, 0, stream>>>(s, heap_bases, mc_base, dst_offset, block_bytes, rank, nranks, syncs, timeout_ns);
-  } else {
-    push_kernel<true, false><<<ctas, kDirectThreads, 0, stream>>>(s, heap_bases, nullptr, dst_offset, block_bytes, rank, nranks, syncs, timeout_ns);
-  }
-  return cudaGetLastError();
+  char* const no_window = nullptr;
+  if (!same_src) return launch_coresident(push_kernel<false, false>, ctas, stream, s, heap_bases, no_window, dst_offset, block_bytes, rank, nranks, syncs, timeout_ns);
+  if (mc_base != nullptr) return launch_coresident(push_kernel<true, true>, ctas, stream, s, heap_bases, mc_base, dst_offset, block_bytes, rank, nranks, syncs, timeout_ns);
+  return launch_coresident(push_kernel<true, false>, ctas, stream, s, heap_bases, no_window, dst_offset, block_bytes, rank, nranks, syncs, timeout_ns);
 }
 
 // One-shot LL collectives on blocks of `bytes` (mode: 0 all-reduce, 1 all-gather, 2 reduce-scatter, 3 all-to-all).

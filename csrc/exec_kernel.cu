@@ -382,7 +382,7 @@ template <typename T, int PROTO, int W>
 __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
   __shared__ int s_fail;
   __shared__ unsigned long long s_decision;        // (tile number << 1) | stored-directly, published by thread 0
-  __shared__ DevStep s_steps[kSmemSteps];
+  __shared__ __align__(16) DevStep s_steps[kSmemSteps];      // filled with 16-byte copies
   const DevTb& tb = a.tbs[a.first_tb + blockIdx.x];
   const RankCtx& me = a.ranks[tb.rank];
   SyncPage* const sync = me.sync;

@@ -73,7 +73,7 @@ enum StepFlags : uint8_t {
   SF_DIRECT_RECV = 2,   // this receive may find its data already stored in (dstbuf, dstoff)
 };
 
-struct DevStep {                // 32 bytes
+struct alignas(16) DevStep {    // 32 bytes, copied as two 16-byte vectors
   uint8_t type, srcbuf, dstbuf, hasdep;
   int16_t depid, deps;          // wait for threadblock depid (of this rank) to finish step deps; -1: none
   int32_t srcoff, dstoff, cnt;  // chunk units, aliases of in-place collectives already resolved
@@ -87,7 +87,7 @@ struct DevStep {                // 32 bytes
   uint16_t opens_before;        // receives opened by this (receive) step itself, after its dependency wait
 };
 
-struct DevTb {                  // 64 bytes
+struct alignas(16) DevTb {      // 64 bytes
   int16_t rank, tb_in_rank, send_peer, recv_peer;
   int32_t chan, nsteps, step_begin;
   int32_t tbs_in_rank;                    // threadblocks this rank runs in the plan
@@ -137,5 +137,7 @@ struct ExecArgs {
   unsigned long long* trace;
   int trace_steps;            // steps per threadblock the trace has room for
 };
+
+static_assert(sizeof(DevStep) == 32 && sizeof(DevTb) == 64, "layout shared with msccl/runtime/plan.py");
 
 }  // namespace msccl

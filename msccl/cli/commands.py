@@ -315,10 +315,22 @@ def make_run(subparsers):
                             help='auto: size-based dispatch (one-shot LL, then kernels on symmetric memory); oneshot / twoshot '
                                  '(all-reduce) / direct: one native kernel; xml: the registered MSCCL-IR plan through the '
                                  'interpreter (also what auto means when --xml is given)')
+        parser.add_argument('--emulate', action='store_true',
+                            help='with --xml: run every rank of the program on ONE GPU (no torchrun), check the result '
+                                 'against the CPU interpreter and print one row per size')
+        parser.add_argument('--trace', type=Path, default=None, metavar='FILE',
+                            help='with --emulate: write per-step device time stamps of the last size to FILE (JSON rows: '
+                                 'rank, tb, step, type, start_ns, end_ns, wait_ns, move_ns)')
+        parser.add_argument('--no-direct', action='store_true',
+                            help='with --emulate: every tile through the FIFOs (no stores into the receivers\' buffers)')
 
     def handle(args):
         if args.command not in ('run', 'bench'):
             return False
+        if getattr(args, 'emulate', False):
+            from msccl.runtime.bench import run_emulated
+            run_emulated(args)
+            return True
         from msccl.runtime.bench import main_from_args
         main_from_args(args, check=(args.command == 'run'))
         return True

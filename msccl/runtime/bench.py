@@ -204,3 +204,73 @@ def main_from_args(args, check=False):
         os.environ.pop('MSCCL_ONESHOT_CTAS', None)
     comm.close()
     dist.destroy_process_group()
+
+
+def run_emulated(args):
+    """``msccl run --xml FILE --emulate``: all ranks of one program on the current GPU.  Every size is first checked bit
+    for bit against the CPU interpreter (up to 1 Mi elements per chunk; larger sizes are timed only), then timed with
+    CUDA events.  ``--trace FILE`` dumps the per-step device time stamps of the last size."""
+    from msccl.interp import input_chunks_of, run_algorithm
+    from msccl.runtime import Communicator, Executor
+    from msccl.xml import load_xml_file
+    if args.xml is None:
+        raise SystemExit('--emulate needs --xml FILE')
+    algo = load_xml_file(args.xml)
+    dtype = _DTYPES[args.dtype]
+    esize = torch.empty((), dtype=dtype).element_size()
+    lo, hi = parse_size(args.min_bytes), parse_size(args.max_bytes)
+    n = algo.ngpus
+    comm = Communicator.emulated(n, fifo_bytes=64 << 20)
+    direct = not getattr(args, 'no_direct', False)
+    try:
+        ex = Executor(comm)
+        plan = ex.compile(algo)
+        chunks_in = max(input_chunks_of(algo, 0), 1)
+        for size in _sizes(lo, hi):
+            chunk = max(1, size // esize // chunks_in)
+            gen = torch.Generator().manual_seed(1)
+            host = [torch.randn(input_chunks_of(algo, r) * chunk, generator=gen).to(dtype) for r in range(n)]
+
+            def place():
+                ins, outs = {}, {}
+                for r in range(n):
+                    if algo.inplace and algo.coll == 'allgather':
+                        full = torch.zeros(algo.gpus[r].o_chunks * chunk, dtype=dtype)
+                        per = input_chunks_of(algo, r) * chunk
+                        full[r * per:(r + 1) * per] = host[r]
+                        ins[r] = full.cuda()
+                    else:
+                        ins[r] = host[r].cuda()
+                        if algo.gpus[r].o_chunks > 0 and not algo.inplace:
+                            outs[r] = torch.zeros(algo.gpus[r].o_chunks * chunk, dtype=dtype, device='cuda')
+                return ins, outs
+
+            ins, outs = place()
+            got = ex.run(plan, ins, outs, direct=direct)
+            ex.check()
+            row = {'algo': algo.name, 'protocol': algo.proto, 'nranks': n, 'chunk_elems': chunk, 'bytes': chunk * chunks_in * esize,
+                   'direct_stores': bool(ex.last_direct_mask), 'threadblocks': plan.grid}
+            if chunk <= (1 << 20):
+                want = run_algorithm(algo, host, chunk, dtype=dtype)
+                row['bit_exact'] = all(torch.equal(got[r].cpu()[:want[r].numel()].view(torch.uint8),
+                                                   want[r][:got[r].numel()].view(torch.uint8)) for r in range(n))
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for _ in range(3):
+                ex.run(plan, ins, outs, direct=direct)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(args.iters):
+                ex.run(plan, ins, outs, direct=direct)
+            stop.record()
+            torch.cuda.synchronize()
+            ex.check()
+            row['time_us'] = round(start.elapsed_time(stop) / args.iters * 1e3, 2)
+            print(json.dumps(row), flush=True)
+        if args.trace is not None:
+            ex.run(plan, ins, outs, direct=direct, trace=True)
+            ex.check()
+            with open(args.trace, 'w') as f:
+                for rec in ex.last_trace():
+                    f.write(json.dumps(rec) + '\n')
+    finally:
+        comm.close()
