@@ -26,6 +26,7 @@
 
 #include "gemm_sm100.cuh"
 #include "gemm_sm100.h"
+#include "fused_reduce.cuh"
 #include "fused_tp.h"
 #include "pipeline_sm100.cuh"
 #include "prims.cuh"
@@ -261,46 +262,6 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_const
 }
 
 // ============================================================ GEMM -> reduce-scatter
-// Sum of the n partial slabs of row block b (rows [b*BM, (b+1)*BM) of this rank's shard), in rank order,
-// fp32 accumulation, one rounding to bf16.  `part` of `parts` CTAs.
-__device__ __forceinline__ void reduce_row_block(const GemmRsArgs& g, const char* my_slabs, size_t slab_bytes, int b, int part,
-                                                 int parts) {
-  constexpr int RU = 4;          // vectors per thread per pass; with 8 sources that is 32 loads in flight
-  const size_t first = static_cast<size_t>(b) * BM * g.N * 2 / 16;
-  const size_t count = static_cast<size_t>(BM) * g.N * 2 / 16;
-  const size_t stride = static_cast<size_t>(parts) * blockDim.x;
-  char* out = static_cast<char*>(g.out);
-  for (size_t i = static_cast<size_t>(part) * blockDim.x + threadIdx.x; i < count; i += stride * RU) {
-    uint4 in[RU][kFusedMaxRanks];
-#pragma unroll
-    for (int u = 0; u < RU; ++u) {
-      const size_t ii = i + u * stride;
-#pragma unroll
-      for (int s = 0; s < kFusedMaxRanks; ++s)
-        if (s < g.nranks && ii < count) in[u][s] = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + (first + ii) * 16);
-    }
-#pragma unroll
-    for (int u = 0; u < RU; ++u) {
-      const size_t ii = i + u * stride;
-      if (ii >= count) break;
-      float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-      for (int s = 0; s < kFusedMaxRanks; ++s) {
-        if (s < g.nranks) {
-          const uint32_t w[4] = {in[u][s].x, in[u][s].y, in[u][s].z, in[u][s].w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            acc8[2 * e] += __uint_as_float(w[e] << 16);
-            acc8[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-          }
-        }
-      }
-      *reinterpret_cast<uint4*>(out + (first + ii) * 16) =
-          make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]), pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
-    }
-  }
-}
-
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmRsArgs g) {
   extern __shared__ uint8_t smem_raw[];
@@ -324,28 +285,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (cta >= ctas) {
     // ------------------------------------------------------------------ reducer CTAs
-    __shared__ int s_ok;
-    const char* my_slabs = g.heap_bases[g.rank] + parity_off;
-    const int part = cta - ctas;
-    for (int i = 0; i < blocks_per_rank; ++i) {
-      const int b = g.reduce_order[i];
-      if (threadIdx.x == 0) s_ok = 1;
-      __syncthreads();
-      if (threadIdx.x < g.nranks) {
-        volatile int never = 0;
-        if (!wait_flag_ge(&page->rs_count[threadIdx.x][b], page->rs_base[threadIdx.x][b] + per_block, &never)) {
-          if (g.error_words != nullptr && atomicCAS(&g.error_words[0], 0, static_cast<int>(GEMM_TIMEOUT_FLAG)) == 0) {
-            g.error_words[1] = blockIdx.x;
-            g.error_words[2] = 3;
-            g.error_words[3] = threadIdx.x * 64 + b;
-          }
-          s_ok = 0;
-        }
-      }
-      __syncthreads();
-      if (s_ok == 0) break;
-      reduce_row_block(g, my_slabs, slab_bytes, b, part, g.reduce_ctas);
-    }
+    reducer_cta(g, page, g.heap_bases[g.rank] + parity_off, slab_bytes, blocks_per_rank, per_block, cta - ctas, g.reduce_ctas);
   } else {
     // ------------------------------------------------------------------ GEMM CTAs
     const Pipe p = carve_smem<3>(smem_raw);
@@ -444,17 +384,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   }
 
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(&page->rs_done, 1u) == gridDim.x - 1u) {
-      // every CTA of this rank is through: the reducers have seen all counters of this launch
-      for (int s = 0; s < g.nranks; ++s)
-        for (int b = 0; b < blocks_per_rank; ++b) page->rs_base[s][b] += per_block;
-      page->rs_done = 0;
-      page->rs_epoch = epoch;
-    }
-  }
+  finish_rs_launch(g, page, blocks_per_rank, per_block, epoch);
 }
 
 }  // namespace

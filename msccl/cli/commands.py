@@ -311,7 +311,7 @@ def make_run(subparsers):
         parser.add_argument('--nccl', action='store_true', help='also time torch.distributed (NCCL) on the same sizes')
         parser.add_argument('--suite', action='store_true',
                             help='all four collectives, direct kernels and registered plans, each verified against NCCL')
-        parser.add_argument('--algo', default='auto', choices=['auto', 'oneshot', 'twoshot', 'direct', 'xml'],
+        parser.add_argument('--algo', default='auto', choices=['auto', 'oneshot', 'twoshot', 'direct', 'xml', 'xmlsym'],
                             help='auto: size-based dispatch (one-shot LL, then kernels on symmetric memory); oneshot / twoshot '
                                  '(all-reduce) / direct: one native kernel; xml: the registered MSCCL-IR plan through the '
                                  'interpreter (also what auto means when --xml is given)')

@@ -49,7 +49,8 @@ def _setup(args, collectives, hi):
     torch.cuda.set_device(local)
     dist.init_process_group('nccl', device_id=torch.device('cuda', local))
     rank, n = dist.get_rank(), dist.get_world_size()
-    comm = Communicator.from_process_group(arena_bytes=hi + (8 << 20))
+    comm = Communicator.from_process_group(arena_bytes=2 * hi + (96 << 20))
+    comm.symmetric_empty(2 * hi + (8 << 20), torch.uint8)      # the two message regions below; what follows is free for plans' scratch
     ex = Executor(comm)
     if args.xml is not None:
         ex.register(load_xml_file(args.xml))
@@ -66,10 +67,18 @@ def _setup(args, collectives, hi):
     return dist, comm, ex, rank, n
 
 
+_NCCL_TIMES = {}
+
+
 def _one_size(dist, comm, ex, rank, n, coll, mode, size, dtype, check, nccl, check_only=False):
-    """One row (dict) for ``coll`` at ``size`` bytes, or None if nothing can run it."""
+    """One row (dict) for ``coll`` at ``size`` bytes, or None if nothing can run it.  ``mode``: auto / oneshot / twoshot /
+    direct (native kernels), xml (registered plan on ordinary tensors: every tile crosses a FIFO), xmlsym (registered
+    plan on tensors from the symmetric arena: stores into the receivers' buffers where the program allows)."""
     esize = torch.empty((), dtype=dtype).element_size()
     unit = n * 16
+    registered = mode == 'xmlsym'
+    if registered:
+        mode = 'xml'
     if mode == 'xml':
         # every chunk of a plan must be a whole number of 16-byte vectors
         probe = ex.select(coll, size if coll != 'allgather' else size // n)
@@ -85,7 +94,7 @@ def _one_size(dist, comm, ex, rank, n, coll, mode, size, dtype, check, nccl, che
         sym = comm.tensor_at(comm.rank, comm.off_arena, numel, dtype)
         src = torch.randn(numel, device='cuda', generator=gen).to(dtype)
         if mode == 'xml':
-            work = src.clone()
+            work = sym if registered else src.clone()
             fn = lambda: ex.all_reduce(work, algorithm='xml')                          # noqa: E731
             if ex.select('allreduce', nbytes) is None:
                 return None
@@ -117,11 +126,20 @@ def _one_size(dist, comm, ex, rank, n, coll, mode, size, dtype, check, nccl, che
             ref_fn = lambda t: dist.all_to_all_single(out, t)                         # noqa: E731
             direct = lambda: ex.all_to_all(sym, src, algorithm=mode)              # noqa: E731
         mine = torch.empty_like(out)
-        if plan is not None:
+        if plan is not None and registered:
+            # output (and for reduce-scatter the input) inside the arena, at the same offset on every rank
+            second = comm.off_arena + ((comm.arena_bytes - (96 << 20)) // 2 + (4 << 20)) // 256 * 256
+            if coll == 'reduce_scatter':
+                sym.copy_(src)
+                src_run, mine = sym, comm.tensor_at(comm.rank, second, out.numel(), dtype)
+            else:
+                src_run, mine = src, comm.tensor_at(comm.rank, second, out.numel(), dtype)
+            fn = lambda: ex.run(plan, src_run, mine)                                   # noqa: E731
+        elif plan is not None:
             fn = lambda: ex.run(plan, src, mine)                                       # noqa: E731
         else:
             fn = direct
-    row = {'collective': coll, 'algo': algo, 'nranks': n, 'bytes': nbytes}
+    row = {'collective': coll, 'algo': algo, 'nranks': n, 'bytes': nbytes, 'memory': 'symmetric' if (registered or mode != 'xml') else 'ordinary'}
     if check:
         if coll == 'allreduce':
             if mode == 'xml':
@@ -154,9 +172,13 @@ def _one_size(dist, comm, ex, rank, n, coll, mode, size, dtype, check, nccl, che
         row['algo'] = ex.last_algorithm                      # what the size-based dispatch picked
     row.update({'time_us': round(ms * 1e3, 2), 'algbw_gbs': round(nbytes / ms / 1e6, 2),
                 'busbw_gbs': round(nbytes * _bus_factor(coll, n) / ms / 1e6, 2)})
+    if mode == 'xml':
+        row['direct_mask'] = ex.last_direct_mask
     if nccl:
-        t = src.clone()
-        nccl_ms = _timed(lambda: ref_fn(t), iters, dist)
+        if (coll, nbytes) not in _NCCL_TIMES:
+            t = src.clone()
+            _NCCL_TIMES[(coll, nbytes)] = _timed(lambda: ref_fn(t), iters, dist)
+        nccl_ms = _NCCL_TIMES[(coll, nbytes)]
         row['nccl_time_us'] = round(nccl_ms * 1e3, 2)
         row['nccl_busbw_gbs'] = round(nbytes * _bus_factor(coll, n) / nccl_ms / 1e6, 2)
     return row
@@ -178,7 +200,7 @@ def main_from_args(args, check=False):
     for coll in collectives:
         mode = getattr(args, 'algo', 'auto')
         if suite:
-            modes = ['auto', 'xml']
+            modes = ['auto', 'xml', 'xmlsym']
         elif mode == 'auto' and args.xml is not None:
             modes = ['xml']
         else:
@@ -187,7 +209,7 @@ def main_from_args(args, check=False):
             for size in _sizes(lo, hi):
                 # the suite verifies each (collective, algorithm) once per size before timing it
                 row = _one_size(dist, comm, ex, rank, n, coll, m, size, dtype, check or suite,
-                                args.nccl and (not suite or m == 'auto') and not check, check_only=check)
+                                args.nccl and not check, check_only=check)
                 if row is not None and rank == 0:
                     print(json.dumps(row), flush=True)
     if suite and n > 2:

@@ -84,6 +84,7 @@ class Executor:
         self._ctx_cache = {}       # emulated mode: buffer pointers of all ranks -> device copy of the rank table
         self.last_direct_mask = 0  # buffers (bit 0 input, 1 output, 2 scratch) the last run() stored into directly
         self._trace = None
+        self._scratch_pool = None  # registered scratch shared by all plans (one process per GPU)
 
     # ------------------------------------------------------------------ plans
     def compile(self, algo_or_xml) -> DevicePlan:
@@ -235,15 +236,21 @@ class Executor:
         return results
 
     def _new_scratch(self, plan, rank, nbytes, device, direct):
-        """Scratch of a plan: inside the symmetric arena when the program receives into scratch and the arena has
-        room (every rank allocates the same sizes in the same order, so the offsets agree), else ordinary memory."""
+        """Scratch of a plan.  When the program receives into scratch, one registered region of the symmetric arena
+        serves all plans of this executor (collectives on one communicator never overlap in time, and every rank
+        grows the region with the same sizes in the same order, so the offsets agree); otherwise, or when the
+        arena has no room, ordinary memory."""
         comm = self.comm
         wants_symmetric = direct and not comm.emulated_mode and 's' in plan.host.direct_bufs.get(rank, ())
         if wants_symmetric:
-            try:
-                return comm.symmetric_empty(nbytes, torch.uint8)[0]
-            except Exception:      # noqa: BLE001 - arena exhausted: the FIFO path needs no registered scratch
-                pass
+            pool = self._scratch_pool
+            if pool is None or pool.numel() < nbytes:
+                try:
+                    pool = self._scratch_pool = comm.symmetric_empty(max(nbytes, 8 << 20), torch.uint8)[0]
+                except Exception:      # noqa: BLE001 - arena exhausted: the FIFO path needs no registered scratch
+                    pool = None
+            if pool is not None:
+                return pool[:nbytes]
         return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
     def last_trace(self):

