@@ -320,6 +320,56 @@ PYBIND11_MODULE(_msccl_native, m) {
     g.reduce_ctas = reduce_ctas;
     check_rt(msccl::sm100::launch_gemm_rs(g, grid, as_stream(stream)), "launch of the fused GEMM reduce-scatter kernel");
   });
+  // The same two kernels on block-scaled fp8 operands (e4m3 values + packed UE8M0 scale blocks).
+  m.def("ag_gemm_mxfp8", [](uintptr_t x_local, uintptr_t sf_local, uintptr_t b, uintptr_t sfb, uintptr_t d, int rows_per_rank, int N,
+                             int K, int ldb, int ldd, int rank, int nranks, int comm_ctas, uintptr_t heap_bases_dev,
+                             std::vector<uintptr_t> heap_ptrs, size_t off_fused, uintptr_t mc_base, size_t gathered_off,
+                             size_t gathered_bytes, uintptr_t error_words, int epilogue, int grid, uintptr_t order, uintptr_t stream) {
+    msccl::sm100::AgGemmF8Args g;
+    std::memset(&g, 0, sizeof(g));
+    g.x_local = reinterpret_cast<const void*>(x_local);
+    g.sf_local = reinterpret_cast<const void*>(sf_local);
+    g.b = reinterpret_cast<const void*>(b);
+    g.sfb = reinterpret_cast<const void*>(sfb);
+    g.d = reinterpret_cast<void*>(d);
+    g.rows_per_rank = rows_per_rank; g.N = N; g.K = K; g.ldb = ldb; g.ldd = ldd;
+    g.rank = rank; g.nranks = nranks; g.comm_ctas = comm_ctas;
+    g.order = reinterpret_cast<const int*>(order);
+    g.heap_bases = reinterpret_cast<char* const*>(heap_bases_dev);
+    if (static_cast<int>(heap_ptrs.size()) != nranks || nranks > msccl::sm100::kFusedMaxRanks) throw std::runtime_error("bad rank count");
+    for (int r = 0; r < nranks; ++r) {
+      g.heap_bases_host[r] = reinterpret_cast<char*>(heap_ptrs[r]);
+      g.pages[r] = reinterpret_cast<msccl::sm100::FusedPage*>(heap_ptrs[r] + off_fused);
+    }
+    g.mc_base = reinterpret_cast<char*>(mc_base);
+    g.gathered_off = gathered_off;
+    g.gathered_bytes = gathered_bytes;
+    g.error_words = reinterpret_cast<int*>(error_words);
+    check_rt(msccl::sm100::launch_ag_gemm_mxfp8(g, epilogue, grid, as_stream(stream)), "launch of the fused fp8 all-gather GEMM kernel");
+  });
+  m.def("gemm_rs_mxfp8", [](uintptr_t a, uintptr_t sfa, uintptr_t b, uintptr_t sfb, uintptr_t out, int rows_per_rank, int N, int K,
+                             int lda, int ldb, int rank, int nranks, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs,
+                             size_t off_fused, size_t partial_off, uintptr_t error_words, int grid, uintptr_t order,
+                             uintptr_t reduce_order, int reduce_ctas, uintptr_t stream) {
+    msccl::sm100::GemmRsF8Args g;
+    std::memset(&g, 0, sizeof(g));
+    g.a = reinterpret_cast<const void*>(a);
+    g.sfa = reinterpret_cast<const void*>(sfa);
+    g.b = reinterpret_cast<const void*>(b);
+    g.sfb = reinterpret_cast<const void*>(sfb);
+    g.out = reinterpret_cast<void*>(out);
+    g.rows_per_rank = rows_per_rank; g.N = N; g.K = K; g.lda = lda; g.ldb = ldb;
+    g.rank = rank; g.nranks = nranks;
+    g.heap_bases = reinterpret_cast<char* const*>(heap_bases_dev);
+    if (static_cast<int>(heap_ptrs.size()) != nranks || nranks > msccl::sm100::kFusedMaxRanks) throw std::runtime_error("bad rank count");
+    for (int r = 0; r < nranks; ++r) g.pages[r] = reinterpret_cast<msccl::sm100::FusedPage*>(heap_ptrs[r] + off_fused);
+    g.partial_off = partial_off;
+    g.error_words = reinterpret_cast<int*>(error_words);
+    g.order = reinterpret_cast<const int*>(order);
+    g.reduce_order = reinterpret_cast<const int*>(reduce_order);
+    g.reduce_ctas = reduce_ctas;
+    check_rt(msccl::sm100::launch_gemm_rs_mxfp8(g, grid, as_stream(stream)), "launch of the fused fp8 GEMM reduce-scatter kernel");
+  });
   m.def("sm_count", &msccl::sm100::sm_count);
   // Fused MoE: phase 0 = dispatch + grouped gate/up GEMM (SwiGLU), phase 1 = grouped down GEMM + combine.
   // geom = [rank, nranks, tokens, topk, hidden, ffn, num_experts, local_experts, cap, comm_ctas]

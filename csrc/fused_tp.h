@@ -60,7 +60,46 @@ struct GemmRsArgs {
   int reduce_ctas;                // CTAs (the last ones of the grid) that only reduce
 };
 
+// Block-scaled fp8 (OCP MX) variants: operands are e4m3 bytes plus UE8M0 scale blocks of 512 bytes per
+// (128 rows, 128 K) in the arrangement tcgen05.cp wants (msccl.ops.gemm.pack_mx_scales).  Tiles are 128 x 128.
+struct AgGemmF8Args {
+  const void* x_local;            // [rows_per_rank, K] e4m3, contiguous
+  const void* sf_local;           // [rows_per_rank/128][K/128][512] scales of x_local
+  const void* b;                  // [N, K] e4m3
+  const void* sfb;                // [N/128][K/128][512]
+  void* d;                        // [nranks*rows_per_rank, N or N/2] bf16
+  int rows_per_rank, N, K, ldb, ldd;
+  int rank, nranks, comm_ctas;
+  const int* order;               // as in AgGemmArgs
+  char* const* heap_bases;
+  char* heap_bases_host[kFusedMaxRanks];
+  FusedPage* pages[kFusedMaxRanks];
+  char* mc_base;
+  size_t gathered_off;            // per parity: [nranks*rows_per_rank, K] values, then [nranks*rows_per_rank/128][K/128][512] scales
+  size_t gathered_bytes;          // bytes of one parity (values + scales, rounded up to 1024)
+  int* error_words;
+};
+
+struct GemmRsF8Args {
+  const void* a;                  // [nranks*rows_per_rank, K] e4m3
+  const void* sfa;                // [nranks*rows_per_rank/128][K/128][512]
+  const void* b;                  // [N, K] e4m3
+  const void* sfb;                // [N/128][K/128][512]
+  void* out;                      // [rows_per_rank, N] bf16: this rank's reduced rows
+  int rows_per_rank, N, K, lda, ldb;
+  int rank, nranks;
+  char* const* heap_bases;
+  FusedPage* pages[kFusedMaxRanks];
+  size_t partial_off;             // the bf16 partial buffer [2][nranks][rows_per_rank, N], as in GemmRsArgs
+  int* error_words;
+  const int* order;
+  const int* reduce_order;
+  int reduce_ctas;
+};
+
 cudaError_t launch_ag_gemm(const AgGemmArgs& args, int epilogue, int grid, cudaStream_t stream);
+cudaError_t launch_ag_gemm_mxfp8(const AgGemmF8Args& args, int epilogue, int grid, cudaStream_t stream);
+cudaError_t launch_gemm_rs_mxfp8(const GemmRsF8Args& args, int grid, cudaStream_t stream);
 cudaError_t launch_gemm_rs(const GemmRsArgs& args, int grid, cudaStream_t stream);
 
 }  // namespace sm100

@@ -86,3 +86,54 @@ class FusedTensorParallel:
                          min(self.reduce_ctas, self.sms - 1), stream_h)
         self.launches += 1
         return out
+
+    # ---------------------------------------------------------------- block-scaled fp8 (OCP MX) operands
+    def all_gather_gemm_mxfp8(self, xq_local, sfx_packed, wq, sfw_packed, epilogue='none', out=None, stream=None):
+        """The all-gather -> GEMM kernel on MX fp8 operands: ``xq_local`` [rows, hidden] e4m3 with its scales packed by
+        ``msccl.ops.gemm.pack_mx_scales(scales, row_multiple=128)``, ``wq`` [N, hidden] e4m3 with packed scales.  What
+        crosses NVLink is the fp8 block plus its scale blocks.  Returns bf16 ``[n*rows, N]`` (``N/2`` with ``swiglu``;
+        gate and up rows interleaved in groups of 64, ``interleave_gate_up(w_gate, w_up, tile=128)``)."""
+        c = self.comm
+        k = self.hidden
+        assert xq_local.shape == (self.rows, k) and xq_local.is_contiguous() and xq_local.dtype == torch.float8_e4m3fn
+        n_out, kw = wq.shape
+        assert kw == k and wq.stride(1) == 1 and wq.dtype == torch.float8_e4m3fn and n_out % 128 == 0 and k % 128 == 0
+        blocks, k_blocks = self.rows // 128, k // 128
+        assert sfx_packed.dtype == torch.uint8 and sfx_packed.numel() == blocks * k_blocks * 512 and sfx_packed.is_contiguous()
+        assert sfw_packed.dtype == torch.uint8 and sfw_packed.numel() >= (n_out // 128) * k_blocks * 512
+        swiglu = epilogue == 'swiglu'
+        cols = n_out // 2 if swiglu else n_out
+        if out is None:
+            out = torch.empty(self.n * self.rows, cols, dtype=torch.bfloat16, device=xq_local.device)
+        per_parity = -(-(self.n * self.rows * k + self.n * blocks * k_blocks * 512) // 1024) * 1024
+        assert per_parity <= self.gathered_bytes
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        c.native.ag_gemm_mxfp8(xq_local.data_ptr(), sfx_packed.data_ptr(), wq.data_ptr(), sfw_packed.data_ptr(), out.data_ptr(),
+                               self.rows, n_out, k, wq.stride(0), out.stride(0), c.rank, self.n, self.comm_ctas,
+                               c.dev_heap_bases, list(c.heap_ptrs), c.off_fused, c.mc_base, self.gathered_off, per_parity,
+                               _errors(xq_local.device).data_ptr(), 1 if swiglu else 0, self.grid or self.sms,
+                               self.ag_order.data_ptr(), stream_h)
+        self.launches += 1
+        return out
+
+    def gemm_reduce_scatter_mxfp8(self, aq, sfa_packed, wq, sfw_packed, out=None, stream=None):
+        """The GEMM -> reduce-scatter kernel on MX fp8 operands: ``aq`` [n*rows, K_shard] e4m3 (scales packed with
+        ``row_multiple=128``), ``wq`` [hidden, K_shard] e4m3.  The partial sums travel and are added up as bf16, as
+        in the bf16 kernel.  Returns this rank's bf16 ``[rows, hidden]``."""
+        c = self.comm
+        m, k = aq.shape
+        assert m == self.n * self.rows and aq.stride(1) == 1 and aq.dtype == torch.float8_e4m3fn and k % 128 == 0
+        assert wq.shape == (self.hidden, k) and wq.stride(1) == 1 and wq.dtype == torch.float8_e4m3fn and self.hidden % 128 == 0
+        assert sfa_packed.dtype == torch.uint8 and sfa_packed.numel() == (m // 128) * (k // 128) * 512
+        assert sfw_packed.dtype == torch.uint8 and sfw_packed.numel() >= (self.hidden // 128) * (k // 128) * 512
+        if out is None:
+            out = torch.empty(self.rows, self.hidden, dtype=torch.bfloat16, device=aq.device)
+        assert out.is_contiguous()
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        c.native.gemm_rs_mxfp8(aq.data_ptr(), sfa_packed.data_ptr(), wq.data_ptr(), sfw_packed.data_ptr(), out.data_ptr(),
+                               self.rows, self.hidden, k, aq.stride(0), wq.stride(0), c.rank, self.n, c.dev_heap_bases,
+                               list(c.heap_ptrs), c.off_fused, self.partial_off, _errors(aq.device).data_ptr(), self.sms,
+                               self.rs_order.data_ptr(), self.reduce_order.data_ptr(), min(self.reduce_ctas, self.sms - 1),
+                               stream_h)
+        self.launches += 1
+        return out

@@ -67,6 +67,46 @@ def check(comm, rank, n, rows, hidden, ffn_shard, calls=3):
         err = (y.float() - want_y).abs().max().item()
         assert err <= 3e-2 * want_y.abs().max().item() + 1e-3, ('gemm_rs', call, err)
     dist.barrier()
+    check_mxfp8(tp, comm, rank, n, rows, hidden, ffn_shard, gen)
+
+
+def check_mxfp8(tp, comm, rank, n, rows, hidden, ffn_shard, gen):
+    """The block-scaled fp8 variants against the fp32 product of the dequantised operands."""
+    from msccl.ops.gemm import dequantize_mxfp8, pack_mx_scales, quantize_mxfp8
+    wg = torch.randn(ffn_shard, hidden, device='cuda', generator=gen) * 0.05
+    wu = torch.randn(ffn_shard, hidden, device='cuda', generator=gen) * 0.05
+    wd = torch.randn(hidden, ffn_shard, device='cuda', generator=gen) * 0.05
+    wgq, wgs = quantize_mxfp8(wg)
+    wuq, wus = quantize_mxfp8(wu)
+    wdq, wds = quantize_mxfp8(wd)
+    # gate and up rows interleaved in groups of 64: the scales are per row, so they interleave the same way
+    guq = interleave_gate_up(wgq.view(torch.uint8), wuq.view(torch.uint8), tile=128).view(torch.float8_e4m3fn)
+    gus = interleave_gate_up(wgs, wus, tile=128)
+    pack = lambda t: pack_mx_scales(t, row_multiple=128)                                  # noqa: E731
+    for call in range(3):
+        x = torch.randn(rows, hidden, device='cuda', generator=gen)
+        xq, xs = quantize_mxfp8(x)
+        x_deq = dequantize_mxfp8(xq, xs)
+        full = torch.empty(n * rows, hidden, device='cuda')
+        dist.all_gather_into_tensor(full, x_deq)
+        plain = tp.all_gather_gemm_mxfp8(xq, pack(xs), wgq, pack(wgs))
+        h = tp.all_gather_gemm_mxfp8(xq, pack(xs), guq, pack(gus), epilogue='swiglu')
+        check_gemm_errors()
+        want_plain = full @ dequantize_mxfp8(wgq, wgs).t()
+        want_h = torch.nn.functional.silu(want_plain) * (full @ dequantize_mxfp8(wuq, wus).t())
+        for got, want, name in ((plain, want_plain, 'ag_gemm_mxfp8'), (h, want_h, 'ag_gemm_mxfp8_swiglu')):
+            err = (got.float() - want).abs().max().item()
+            assert err <= 2e-2 * want.abs().max().item() + 1e-3, (name, call, err)
+        hq, hs = quantize_mxfp8(h.float())
+        y = tp.gemm_reduce_scatter_mxfp8(hq, pack(hs), wdq, pack(wds))
+        check_gemm_errors()
+        partial = dequantize_mxfp8(hq, hs) @ dequantize_mxfp8(wdq, wds).t()
+        partial = partial.bfloat16().float()                    # the partial sums travel as bf16
+        dist.all_reduce(partial)
+        want_y = partial[rank * rows:(rank + 1) * rows]
+        err = (y.float() - want_y).abs().max().item()
+        assert err <= 3e-2 * want_y.abs().max().item() + 1e-3, ('gemm_rs_mxfp8', call, err)
+    dist.barrier()
 
 
 def bench(comm, rank, n, tokens, hidden, ffn, iters):
