@@ -430,11 +430,13 @@ def run_ours_one_gpu(args, local):
     plan = ex.compile(algo)
     numel = nbytes // esize
     # verification on a small case of the same program against the CPU interpreter (bit exact)
+    from msccl.interp import input_chunks_of
     gen = torch.Generator().manual_seed(0)
-    small = [torch.randn(world * 4096, generator=gen).to(dtype) for _ in range(world)]
+    small_chunk = 4096
+    small = [torch.randn(input_chunks_of(algo, r) * small_chunk, generator=gen).to(dtype) for r in range(world)]
     got = ex.run(plan, {r: small[r].cuda() for r in range(world)})
     ex.check()
-    want = run_algorithm(algo, small, 4096, dtype=dtype)
+    want = run_algorithm(algo, small, small_chunk, dtype=dtype)
     verified = all(torch.equal(got[r].cpu().view(torch.int16), want[r].view(torch.int16)) for r in range(world))
     bufs = {r: (torch.randn(numel, device='cuda', dtype=torch.float32) * 0.01).to(dtype) for r in range(world)}
     pinned = (torch.randn(numel, dtype=torch.float32) * 0.01).to(dtype).pin_memory()

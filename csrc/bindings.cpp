@@ -96,11 +96,11 @@ void clear_status(uintptr_t sync_page) {
 // width]; `bufs` = [in, out, scratch] pointers of the launching rank (one rank per process; empty in emulation, where the
 // rank table carries them) and `elems` their sizes in elements; `peer_heaps` / `sym_off` / `direct_mask` describe which of
 // the buffers lie at the same offset of every rank's symmetric heap (stores straight into a peer's buffer); `trace` is 0
-// or a zeroed device array of grid x trace_steps x 4 words.
+// or a zeroed device array of grid x trace_steps x 6 words.
 void launch(uintptr_t tbs, uintptr_t steps, uintptr_t ranks, const std::vector<long long>& geom, unsigned long long timeout_ns,
             uintptr_t stream, bool cooperative, const std::vector<uintptr_t>& bufs, const std::vector<long long>& elems,
             const std::vector<uintptr_t>& peer_heaps, const std::vector<long long>& sym_off, int direct_mask,
-            unsigned long long epoch_base, uintptr_t trace, int trace_steps) {
+            unsigned long long epoch_base, uintptr_t trace, int trace_steps, int wait_mode) {
   if (geom.size() != 10) throw std::runtime_error("launch: geometry vector must have 10 entries");
   if (!bufs.empty() && (bufs.size() != 3 || elems.size() != 3)) throw std::runtime_error("launch: three buffers and three sizes");
   if (peer_heaps.size() > static_cast<size_t>(msccl::kMaxRanks) || (!sym_off.empty() && sym_off.size() != 3))
@@ -128,6 +128,7 @@ void launch(uintptr_t tbs, uintptr_t steps, uintptr_t ranks, const std::vector<l
   a.epoch_base = epoch_base;
   a.trace = reinterpret_cast<unsigned long long*>(trace);
   a.trace_steps = trace_steps;
+  a.wait_mode = wait_mode;
   check_rt(msccl::launch_exec(a, static_cast<int>(geom[7]), static_cast<int>(geom[8]), static_cast<int>(geom[9]),
                               static_cast<int>(geom[6]), as_stream(stream), cooperative),
            "launch of the MSCCL-IR executor kernel");
@@ -201,7 +202,7 @@ PYBIND11_MODULE(_msccl_native, m) {
         py::arg("stream"), py::arg("cooperative"), py::arg("bufs") = std::vector<uintptr_t>(),
         py::arg("elems") = std::vector<long long>(), py::arg("peer_heaps") = std::vector<uintptr_t>(),
         py::arg("sym_off") = std::vector<long long>(), py::arg("direct_mask") = 0, py::arg("epoch_base") = 0ull,
-        py::arg("trace") = 0, py::arg("trace_steps") = 0);
+        py::arg("trace") = 0, py::arg("trace_steps") = 0, py::arg("wait_mode") = 0);
   m.def("max_coresident_ctas", &msccl::max_coresident_ctas);
 
   m.def("vmm_granularity", &msccl::vmm_granularity);

@@ -16,9 +16,9 @@
 // bounded: when the deadline passes the CTA records what it was waiting for in the rank's status words,
 // raises the rank's abort flag and returns.
 //
-// Waiting is done per warp (lane 0 of every warp polls the flags its step needs), data movement follows
-// without a CTA-wide barrier in between, and one barrier per step separates the movement from the signals
-// thread 0 sends afterwards while the other warps already poll for the next step.
+// Thread 0 of a CTA does the waiting: it polls the flags its step needs and hands its verdict to the other
+// warps; after the data movement one barrier separates it from the signals thread 0 sends - one system-scope
+// fence per step, the flags themselves relaxed stores behind it.
 //
 // Large buffers are processed in iterations: iteration k handles elements [k*tile, (k+1)*tile) of every
 // chunk, so one program serves any message size.  Chunks that are not multiples of 16 bytes run on
@@ -381,7 +381,7 @@ __device__ __forceinline__ bool is_recv(int t) {
 template <typename T, int PROTO, int W>
 __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
   __shared__ int s_fail;
-  __shared__ unsigned long long s_decision;        // (tile number << 1) | stored-directly, published by thread 0
+  __shared__ unsigned long long s_decision;        // (pass << 3) | failed | data in place | store in place: thread 0's verdict
   __shared__ __align__(16) DevStep s_steps[kSmemSteps];      // filled with 16-byte copies
   const DevTb& tb = a.tbs[a.first_tb + blockIdx.x];
   const RankCtx& me = a.ranks[tb.rank];
@@ -446,11 +446,12 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
     st_release_sys(recv_open, opened);
   }
   unsigned int mode_bits = 0;                      // thread 0: how the last kFifoSlots tiles were sent
+  unsigned long long pass = 0;                     // steps executed so far by this CTA (tags the verdicts of thread 0)
   __syncthreads();
 
   const long long C = a.chunk_elems;
   const bool trace_on = a.trace != nullptr;
-  unsigned long long* const trace = trace_on ? a.trace + static_cast<long long>(a.first_tb + blockIdx.x) * a.trace_steps * 4 : nullptr;
+  unsigned long long* const trace = trace_on ? a.trace + static_cast<long long>(a.first_tb + blockIdx.x) * a.trace_steps * 6 : nullptr;
   bool failed = false;
 
   for (int it = 0; it < a.iterations && !failed; ++it) {
@@ -496,10 +497,16 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
         if (sk.type == ST_RE && (static_cast<long long>(sk.srcoff) + sk.cnt) * C > elems[sk.srcbuf]) { in_bounds = false; worst = sk.srcoff; }
       }
 
-      // ---- waits (lane 0 of every warp) ----
+      // ---- waits ----
+      // Thread 0 polls the flags in global memory (one poller per CTA: sixteen would only fight over the same lines in
+      // L2) and leaves its verdict - go or failed, and which way the tile travels - in shared memory with a running
+      // number, so it is never mistaken for the previous step's.  The other warps pick it up at a CTA barrier
+      // (wait_mode 1, the default: parked warps cost nothing) or by polling shared memory (wait_mode 0: no barrier
+      // before the movement, but measured slower - the pollers take issue slots from thread 0).
       unsigned int code = 0, aux0 = 0, aux1 = 0;
       bool direct_send = false, direct_recv = false;
-      if (lane == 0) {
+      ++pass;
+      if (tid == 0) {
         if (!in_bounds) {
           code = STATUS_BOUNDS; aux0 = st.type; aux1 = static_cast<unsigned int>(worst);
         }
@@ -513,24 +520,12 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
             !w.until_ge(&sync->send_head[send_conn], sseq + 1 > kFifoSlots ? sseq + 1 - kFifoSlots : 0, true)) {
           code = STATUS_TIMEOUT_CREDIT; aux0 = send_peer_id; aux1 = chan;
         }
-        if (code == 0 && can_direct_send) {
-          // One decision per tile for the whole CTA: thread 0 looks whether the receiver has opened the slot and
-          // publishes the verdict in shared memory; the other warps pick it up there.
-          if (tid == 0) {
-            direct_send = ld_acquire_sys(&sync->recv_posted[send_conn]) >= sseq + 1;
-            *reinterpret_cast<volatile unsigned long long*>(&s_decision) = ((sseq + 1) << 1) | (direct_send ? 1ull : 0ull);
-          } else {
-            unsigned int spins = 0;
-            unsigned long long d;
-            while (((d = *reinterpret_cast<volatile unsigned long long*>(&s_decision)) >> 1) != sseq + 1) {
-              if ((++spins & 1023u) == 0 && w.expired()) { code = STATUS_ABORTED; break; }
-            }
-            direct_send = (d & 1ull) != 0;
-          }
-        }
+        // store this tile straight into the receiver's slot?  Only if the receiver has opened it by now.
+        if (code == 0 && can_direct_send) direct_send = ld_acquire_sys(&sync->recv_posted[send_conn]) >= sseq + 1;
         if (code == 0 && recvs && PROTO == PROTO_SIMPLE) {
-          // (thread 0 only: it has passed the barrier that ended the previous step and this step's dependency wait)
-          if (opening && !eager && tid == 0 && st.opens_before > 0) {
+          // a receive that opens its own slot does so here: the barrier that ended the previous step and this step's
+          // dependency wait are behind us
+          if (opening && !eager && st.opens_before > 0) {
             opened += st.opens_before;
             st_release_sys(recv_open, opened);
           }
@@ -544,6 +539,20 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
           record_failure(sync, code, my_rank, my_tb, s, it, aux0, aux1);
           *reinterpret_cast<volatile int*>(&s_fail) = 1;
         }
+        *reinterpret_cast<volatile unsigned long long*>(&s_decision) =
+            (pass << 3) | (code != 0 ? 4ull : 0ull) | (direct_recv ? 2ull : 0ull) | (direct_send ? 1ull : 0ull);
+      }
+      if (a.wait_mode == 1) __syncthreads();
+      if (tid != 0 && lane == 0) {
+        unsigned int spins = 0;
+        unsigned long long d;
+        while (((d = *reinterpret_cast<volatile unsigned long long*>(&s_decision)) >> 3) != pass) {
+          __nanosleep(64);         // a busy loop here takes issue slots from thread 0's polling and from the signals
+          if ((++spins & 4095u) == 0 && w.expired()) { d = 4ull; break; }
+        }
+        code = (d & 4ull) ? static_cast<unsigned int>(STATUS_ABORTED) : 0u;
+        direct_recv = (d & 2ull) != 0;
+        direct_send = (d & 1ull) != 0;
       }
       code = __shfl_sync(kFullWarp, code, 0);
       direct_send = __shfl_sync(kFullWarp, direct_send ? 1 : 0, 0) != 0;
@@ -632,6 +641,8 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
         }
       }
       __syncthreads();
+      unsigned long long t_moved = 0;
+      if (trace_on && tid == 0) t_moved = global_timer_ns();
       if (*reinterpret_cast<volatile int*>(&s_fail) != 0) {
         // a wait or a flag-in-data poll ran out of time (the first failure recorded wins)
         if (tid == 0) record_failure(sync, STATUS_TIMEOUT_DATA, my_rank, my_tb, s, it, recv_peer_id, chan);
@@ -641,34 +652,40 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
 
       // ---- signals (one thread; the other warps go on to the next step's waits) ----
       if (tid == 0) {
-        if (sends && PROTO == PROTO_SIMPLE) {
+        // One fence covers everything this step publishes (a system-scope fence costs microseconds, so the flags
+        // themselves are relaxed stores behind it): the tile written by all warps before the barrier comes before
+        // its count; this rank's own accesses to a slot come before the slot is opened; the step's stores come
+        // before the progress word other threadblocks wait on.  The credit alone needs no fence: every warp has used
+        // what it read from the FIFO slot before it came to the barrier.
+        unsigned int more = 0;
+        bool any_dep = st.hasdep != 0;
+        if (opening && !eager) more = st.opens_after;
+        for (int k = 1; k < nb; ++k) {
+          if (opening && !eager) more += sp[s + k].opens_after;
+          any_dep = any_dep || sp[s + k].hasdep != 0;
+        }
+        const bool publishes_tile = sends && PROTO == PROTO_SIMPLE;
+        if (publishes_tile || more > 0) __threadfence_system();
+        else if (any_dep) __threadfence();
+        if (publishes_tile) {
           const unsigned int bit = 1u << static_cast<int>(sseq % kFifoSlots);
           mode_bits = direct_send ? (mode_bits | bit) : (mode_bits & ~bit);
-          __threadfence_system();
-          st_release_sys(send_tail, (static_cast<unsigned long long>(mode_bits) << kTailModeShift) | (sseq + 1));
+          st_relaxed_sys(send_tail, (static_cast<unsigned long long>(mode_bits) << kTailModeShift) | (sseq + 1));
         }
-        if (opening && !eager) {
-          unsigned int more = st.opens_after;
-          for (int k = 1; k < nb; ++k) more += sp[s + k].opens_after;
-          if (more > 0) {
-            opened += more;
-            st_release_sys(recv_open, opened);
-          }
+        if (more > 0) {
+          opened += more;
+          st_relaxed_sys(recv_open, opened);
         }
-        if (recvs) st_release_sys(recv_credit, rseq + 1);
-        bool any_dep = st.hasdep != 0;
-        for (int k = 1; k < nb; ++k) any_dep = any_dep || sp[s + k].hasdep != 0;
-        if (any_dep) {
-          __threadfence();
-          st_release_gpu(&sync->progress[my_tb], pack_progress(epoch, it, last + 1));
-        }
+        if (recvs) st_relaxed_sys(recv_credit, rseq + 1);
+        if (any_dep) st_relaxed_gpu(&sync->progress[my_tb], pack_progress(epoch, it, last + 1));
         if (trace_on && s < a.trace_steps) {
           const unsigned long long t2 = global_timer_ns();
-          unsigned long long* rec = trace + static_cast<long long>(s) * 4;
+          unsigned long long* rec = trace + static_cast<long long>(s) * 6;
           if (it == 0) rec[0] = t0;
           rec[1] = t2;
           rec[2] += t1 - t0;
-          rec[3] += t2 - t1;
+          rec[3] += t_moved - t1;
+          rec[4] += t2 - t_moved;
         }
       }
       if (sends) ++sseq;

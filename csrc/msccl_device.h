@@ -133,7 +133,9 @@ struct ExecArgs {
   char* peer_heap[kMaxRanks];
   long long sym_off[3];
   int direct_mask;
-  // Optional step trace: 4 words per (threadblock, step): first start, last end, total ns waiting, total ns moving.
+  int wait_mode;              // 0: warps pick up thread 0's verdict by polling shared memory; 1: at a CTA barrier
+  // Optional step trace: 6 words per (threadblock, step): first start, last end, total ns waiting, moving (up to the
+  // barrier that ends the step) and signalling; the sixth word is spare.
   unsigned long long* trace;
   int trace_steps;            // steps per threadblock the trace has room for
 };

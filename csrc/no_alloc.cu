@@ -289,6 +289,7 @@ __attribute__((visibility("default"))) int msccl_exec_noalloc(
   a.first_tb = 0;
   a.bufs_from_args = 0;
   a.epoch_base = epoch_base;
+  a.wait_mode = 1;
   a.direct_mask = 7;            // all ranks live on this device: every buffer can be stored into directly
   for (int b = 0; b < 3; ++b) a.sym_off[b] = -1;
   e = launch_exec(a, dtype, proto, width, num_tbs, stream, true);

@@ -20,6 +20,7 @@ def register_b200_plans():
     # NVLink port; all threadblocks of a plan must also be co-resident (148 SMs).
     copies = {2: 32, 4: 16, 8: 8}
     small = {2: 4, 4: 2, 8: 1}     # latency-bound sizes: flag-in-data packets, few CTAs
+    middle = {2: 16, 4: 8, 8: 4}   # between the two: 128-byte lines with 120 bytes of payload (LL128), no fence per tile
     for n in B200_GPU_COUNTS:
         mtype = f'b200x{n}' if n != 8 else ['b200', 'b200x8']
         box = fully_connected(n)
@@ -38,11 +39,19 @@ def register_b200_plans():
                                sizes=('256KB', None), instances=copies[n], threadblock_policy=manual,
                                machines=lambda m: m == 1)(two_shot)
 
+        def two_shot_ll128(prog, nodes, n=n):
+            allreduce_two_shot(n)
+        two_shot_ll128.__name__ = f'b200_allreduce_two_shot_ll128_{n}'
+        register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='LL128',
+                               sizes=('256KB', '4MB'), instances=middle[n], threadblock_policy=manual,
+                               machines=lambda m: m == 1)(two_shot_ll128)
+
         def a2a(prog, nodes, n=n):
             alltoall_direct(n)
         a2a.__name__ = f'b200_alltoall_direct_{n}'
         register_msccl_program(box, 'alltoall', mtype, chunk_factor=1, protocol='Simple', instances=copies[n],
                                sizes=('512KB', None), machines=lambda m: m == 1)(a2a)
+
 
         def a2a_ll(prog, nodes, n=n):
             alltoall_direct(n)
@@ -73,3 +82,22 @@ def register_b200_plans():
         rs_ll.__name__ = f'b200_reduce_scatter_direct_ll_{n}'
         register_msccl_program(box, 'reduce_scatter', mtype, chunk_factor=1, protocol='LL', instances=small[n],
                                sizes=(0, '512KB'), machines=lambda m: m == 1)(rs_ll)
+
+        # registered last: on equal ranges the later registration wins
+        def a2a_ll128(prog, nodes, n=n):
+            alltoall_direct(n)
+        a2a_ll128.__name__ = f'b200_alltoall_direct_ll128_{n}'
+        register_msccl_program(box, 'alltoall', mtype, chunk_factor=1, protocol='LL128', instances=middle[n],
+                               sizes=('512KB', '8MB'), machines=lambda m: m == 1)(a2a_ll128)
+
+        def ag_ll128(prog, nodes, n=n):
+            allgather_direct(n)
+        ag_ll128.__name__ = f'b200_allgather_direct_ll128_{n}'
+        register_msccl_program(box, 'allgather', mtype, chunk_factor=1, protocol='LL128', instances=middle[n],
+                               sizes=('512KB', '8MB'), machines=lambda m: m == 1)(ag_ll128)
+
+        def rs_ll128(prog, nodes, n=n):
+            reduce_scatter_direct(n)
+        rs_ll128.__name__ = f'b200_reduce_scatter_direct_ll128_{n}'
+        register_msccl_program(box, 'reduce_scatter', mtype, chunk_factor=1, protocol='LL128', instances=middle[n],
+                               sizes=('512KB', '8MB'), machines=lambda m: m == 1)(rs_ll128)

@@ -84,6 +84,8 @@ class Executor:
         self._ctx_cache = {}       # emulated mode: buffer pointers of all ranks -> device copy of the rank table
         self.last_direct_mask = 0  # buffers (bit 0 input, 1 output, 2 scratch) the last run() stored into directly
         self._trace = None
+        # how the warps of a CTA learn that a step may start: 'poll' shared memory, or at a CTA 'barrier'
+        self.wait_mode = 0 if os.environ.get('MSCCL_EXEC_WAIT', 'barrier') == 'poll' else 1
         self._scratch_pool = None  # registered scratch shared by all plans (one process per GPU)
 
     # ------------------------------------------------------------------ plans
@@ -204,7 +206,7 @@ class Executor:
         trace_ptr, trace_steps = 0, 0
         if trace:
             trace_steps = max(1, max(len(tb.steps) for g in algo.gpus for tb in g.tbs))
-            self._trace = torch.zeros(plan.grid * trace_steps * 4, dtype=torch.int64, device=first.device)
+            self._trace = torch.zeros(plan.grid * trace_steps * 6, dtype=torch.int64, device=first.device)
             self._trace_shape = (plan, trace_steps)
             trace_ptr = self._trace.data_ptr()
         geom = [chunk, tile, plan.slot_bytes, iterations, comm.world, 0, plan.grid, key[0], proto, width]
@@ -219,7 +221,7 @@ class Executor:
                 rankctx = self._ctx_cache[table] = nat.upload(comm.rankctx_bytes(buffers, sizes))
             self.last_direct_mask = 7 if direct else 0
             nat.launch(plan.dev_tbs, plan.dev_steps, rankctx, geom, comm.timeout_ns, stream_h, self.cooperative,
-                       direct_mask=self.last_direct_mask, trace=trace_ptr, trace_steps=trace_steps)
+                       direct_mask=self.last_direct_mask, trace=trace_ptr, trace_steps=trace_steps, wait_mode=self.wait_mode)
         else:
             r = comm.rank
             sym_off, mask = [-1, -1, -1], 0
@@ -231,7 +233,7 @@ class Executor:
             self.last_direct_mask = mask
             nat.launch(plan.dev_tbs, plan.dev_steps, comm.dev_rankctx, geom, comm.timeout_ns, stream_h, self.cooperative,
                        bufs=list(buffers[r]), elems=list(sizes[r]), peer_heaps=list(comm.heap_ptrs), sym_off=sym_off,
-                       direct_mask=mask, trace=trace_ptr, trace_steps=trace_steps)
+                       direct_mask=mask, trace=trace_ptr, trace_steps=trace_steps, wait_mode=self.wait_mode)
         self.launches += 1
         return results
 
@@ -255,22 +257,22 @@ class Executor:
 
     def last_trace(self):
         """Step trace of the last ``run(..., trace=True)``: one dict per (rank, threadblock, step) with the first start
-        and last end (ns of the GPU's global timer, relative to the earliest start) and the total ns spent waiting
-        and moving data over all iterations."""
+        and last end (ns of the GPU's global timer, relative to the earliest start) and the total ns spent waiting,
+        moving data (up to the barrier that ends the step) and signalling over all iterations."""
         if getattr(self, '_trace', None) is None:
             return []
         plan, steps = self._trace_shape
-        raw = self._trace.cpu().view(-1, steps, 4)
+        raw = self._trace.cpu().view(-1, steps, 6)
         starts = raw[:, :, 0][raw[:, :, 0] > 0]
         origin = int(starts.min()) if starts.numel() else 0
         rows, cta = [], 0
         for r in self.comm.local_ranks:
             for tb in plan.algo.gpus[r].tbs:
                 for si, st in enumerate(tb.steps):
-                    t0, t1, wait, move = (int(v) for v in raw[cta, si])
+                    t0, t1, wait, move, signal, _ = (int(v) for v in raw[cta, si])
                     if t1 or t0:
                         rows.append({'rank': r, 'tb': tb.id, 'step': si, 'type': st.type, 'start_ns': t0 - origin,
-                                     'end_ns': t1 - origin, 'wait_ns': wait, 'move_ns': move})
+                                     'end_ns': t1 - origin, 'wait_ns': wait, 'move_ns': move, 'signal_ns': signal})
                 cta += 1
         return rows
 

@@ -134,6 +134,40 @@ def main():
         comm.mc_base = saved
         dist.barrier()
 
+    # 3a. programs made of in-switch steps (msccl.language.ext_nvls) are handed to the native multimem kernels
+    if comm.mc_base:
+        from msccl.language.ext_nvls import allgather_nvls, allreduce_nvls, reduce_scatter_nvls
+        count = n * 8192
+        view = sym[:count]
+        view.copy_(parts[rank][:count].cuda())
+        torch.cuda.synchronize()
+        dist.barrier()
+        out = ex.run(ex.compile(allreduce_nvls(n, 4)), view)[rank]
+        ex.check()
+        assert ex.last_algorithm == 'in-switch allreduce' and out.data_ptr() == view.data_ptr()
+        ref64 = sum(p[:count].double() for p in parts)
+        assert torch.allclose(view.cpu().double(), ref64, rtol=2e-2, atol=2e-2)
+        dist.barrier()
+        # reduce-scatter: my slice of the sum, to ordinary memory
+        view.copy_(parts[rank][:count].cuda())
+        torch.cuda.synchronize()
+        dist.barrier()
+        mine = ex.run(ex.compile(reduce_scatter_nvls(n, 2)), view)[rank]
+        ex.check()
+        assert torch.allclose(mine.cpu().double(), ref64[rank * 8192:(rank + 1) * 8192], rtol=2e-2, atol=2e-2)
+        dist.barrier()
+        # all-gather in place: my block already sits at its position
+        view.zero_()
+        view[rank * 8192:(rank + 1) * 8192].copy_(parts[rank][:8192].cuda())
+        torch.cuda.synchronize()
+        dist.barrier()
+        ex.run(ex.compile(allgather_nvls(n)), view)
+        ex.check()
+        assert torch.equal(view.cpu(), torch.cat([p[:8192] for p in parts]))
+        dist.barrier()
+        if rank == 0:
+            print('in-switch programs: executed by the multimem kernels', flush=True)
+
     # 3b. direct all-gather / all-to-all / reduce-scatter on symmetric memory (sizes with a ragged tail per CTA)
     for blk in (2048, 1 << 16, (1 << 18) + 4096):
         total = blk * n

@@ -126,8 +126,11 @@ def test_init_b200_plan_table(capsys, clean_env):
     msccl.init('b200', 1, ('allreduce', (0, None)), ('alltoall', '1MB'), ('allgather', '64KB'))
     out = capsys.readouterr().out
     assert 'b200_allreduce_one_shot_8 with LL protocol' in out and 'b200_allreduce_two_shot_8' in out
+    assert 'b200_allreduce_two_shot_ll128_8 with LL128 protocol' in out          # 128-byte lines between the two
+    assert 'b200_alltoall_direct_ll128_8 with LL128 protocol' in out
     root = ET.parse(os.environ['MSCCL_CONFIG']).getroot()
-    assert root.tag == 'msccl_algos' and len(root.findall('load')) == 4
+    assert root.tag == 'msccl_algos' and len(root.findall('load')) == 5
+    assert [e.get('proto') for e in root.findall('load')].count('LL128') == 2
     for entry in load_plan_table(os.environ['MSCCL_CONFIG']):
         assert validate(entry.algo) == [] and entry.algo.ngpus == 8
 
