@@ -25,7 +25,7 @@ cudaError_t launch_exec(const ExecArgs& args, int dtype, int proto, int width, i
 int max_coresident_ctas(int dtype, int proto, int width);
 cudaError_t launch_twoshot_allreduce(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int dtype,
                                      int rank, int nranks, SyncPage* const* syncs, unsigned long long timeout_ns, int ctas,
-                                     cudaStream_t stream, void* rs_out);
+                                     cudaStream_t stream, void* rs_out, bool pipelined);
 cudaError_t launch_push(const void* src, bool same_src, char* const* heap_bases, char* mc_base, long long dst_offset,
                         long long block_bytes, int rank, int nranks, SyncPage* const* syncs, unsigned long long timeout_ns,
                         int ctas, cudaStream_t stream);
@@ -409,14 +409,15 @@ PYBIND11_MODULE(_msccl_native, m) {
   // selects peer loads/stores, otherwise the NVLink multicast window is used.
   m.def("twoshot_allreduce", [](uintptr_t heap_bases_dev, uintptr_t mc_base, long long offset, long long bytes, int dtype,
                                  int rank, int nranks, uintptr_t syncs_dev, unsigned long long timeout_ns, int ctas,
-                                 uintptr_t stream, uintptr_t rs_out) {
+                                 uintptr_t stream, uintptr_t rs_out, bool pipelined) {
     check_rt(msccl::launch_twoshot_allreduce(reinterpret_cast<char* const*>(heap_bases_dev), reinterpret_cast<char*>(mc_base),
                                              offset, bytes, dtype, rank, nranks,
                                              reinterpret_cast<SyncPage* const*>(syncs_dev), timeout_ns, ctas, as_stream(stream),
-                                             reinterpret_cast<void*>(rs_out)),
+                                             reinterpret_cast<void*>(rs_out), pipelined),
              "launch of the two-shot all-reduce kernel");
   }, py::arg("heap_bases"), py::arg("mc_base"), py::arg("offset"), py::arg("bytes"), py::arg("dtype"), py::arg("rank"),
-     py::arg("nranks"), py::arg("syncs"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("stream"), py::arg("rs_out") = 0);
+     py::arg("nranks"), py::arg("syncs"), py::arg("timeout_ns"), py::arg("ctas"), py::arg("stream"), py::arg("rs_out") = 0,
+     py::arg("pipelined") = false);
   // All-gather (same_src) or all-to-all: store this rank's block(s) into block `rank` of the buffer
   // at `dst_offset` of every rank's symmetric heap.  mc_base != 0 (all-gather only) uses multimem.st.
   m.def("push_blocks", [](uintptr_t src, bool same_src, uintptr_t heap_bases_dev, uintptr_t mc_base, long long dst_offset,

@@ -111,7 +111,9 @@ template <> struct Multimem<__half> {
 // ---- two-shot, in place on a symmetric buffer ---------------------------------------------
 // heap_bases[r] + offset = rank r's buffer as mapped here (P2P mode); mc = the same offset inside
 // the multicast window (NVLS mode).
-template <typename T, bool NVLS>
+// PIPE (NVLS only): the in-switch loads of the next sweep are issued before the stores of the current one, so
+// that reduction and broadcast traffic overlap inside every thread instead of alternating.
+template <typename T, bool NVLS, bool PIPE>
 __global__ void __launch_bounds__(kDirectThreads, 1)
 twoshot_allreduce_kernel(char* const* heap_bases, char* mc, long long offset, long long bytes, int rank, int nranks,
                          SyncPage* const* syncs, unsigned long long timeout_ns, char* rs_out) {
@@ -127,7 +129,34 @@ twoshot_allreduce_kernel(char* const* heap_bases, char* mc, long long offset, lo
   const long long per_cta = (r_end - r_begin + gridDim.x - 1) / gridDim.x;
   const long long begin = min(r_end, r_begin + per_cta * blockIdx.x), end = min(r_end, begin + per_cta);
 
-  if (NVLS) {
+  if (NVLS && PIPE) {
+    constexpr int U = 8;
+    const long long stride = static_cast<long long>(blockDim.x) * U;
+    uint4 cur[U], nxt[U];
+    long long v = begin + threadIdx.x;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = v + static_cast<long long>(u) * blockDim.x;
+      if (i < end) cur[u] = Multimem<T>::ld_reduce(mc + i * 16);
+    }
+    for (; v < end; v += stride) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = v + stride + static_cast<long long>(u) * blockDim.x;
+        if (i < end) nxt[u] = Multimem<T>::ld_reduce(mc + i * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = v + static_cast<long long>(u) * blockDim.x;
+        if (i < end) {
+          if (rs_out != nullptr) *reinterpret_cast<uint4*>(rs_out + (i - r_begin) * 16) = cur[u];
+          else Multimem<T>::st(mc + i * 16, cur[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) cur[u] = nxt[u];
+    }
+  } else if (NVLS) {
     constexpr int U = 8;
     for (long long v = begin + threadIdx.x; v < end; v += static_cast<long long>(blockDim.x) * U) {
       uint4 acc[U];
@@ -360,13 +389,18 @@ cudaError_t launch_coresident(void (*kernel)(Params...), int ctas, cudaStream_t 
 
 template <typename T>
 cudaError_t twoshot_typed(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int rank, int nranks,
-                          SyncPage* const* syncs, unsigned long long timeout_ns, int ctas, cudaStream_t stream, char* rs_out) {
-  if (mc_base != nullptr) {
-    return launch_coresident(twoshot_allreduce_kernel<T, true>, ctas, stream, heap_bases, mc_base + offset, offset, bytes, rank,
-                             nranks, syncs, timeout_ns, rs_out);
+                          SyncPage* const* syncs, unsigned long long timeout_ns, int ctas, cudaStream_t stream, char* rs_out,
+                          bool pipelined) {
+  if (mc_base != nullptr && pipelined) {
+    return launch_coresident(twoshot_allreduce_kernel<T, true, true>, ctas, stream, heap_bases, mc_base + offset, offset, bytes,
+                             rank, nranks, syncs, timeout_ns, rs_out);
   }
-  return launch_coresident(twoshot_allreduce_kernel<T, false>, ctas, stream, heap_bases, static_cast<char*>(nullptr), offset, bytes,
-                           rank, nranks, syncs, timeout_ns, rs_out);
+  if (mc_base != nullptr) {
+    return launch_coresident(twoshot_allreduce_kernel<T, true, false>, ctas, stream, heap_bases, mc_base + offset, offset, bytes,
+                             rank, nranks, syncs, timeout_ns, rs_out);
+  }
+  return launch_coresident(twoshot_allreduce_kernel<T, false, false>, ctas, stream, heap_bases, static_cast<char*>(nullptr), offset,
+                           bytes, rank, nranks, syncs, timeout_ns, rs_out);
 }
 
 // mode: 0 all-reduce, 1 all-gather, 2 reduce-scatter, 3 all-to-all
@@ -386,15 +420,15 @@ cudaError_t oneshot_typed(const void* in, void* out, char* const* staging, long 
 
 cudaError_t launch_twoshot_allreduce(char* const* heap_bases, char* mc_base, long long offset, long long bytes, int dtype,
                                      int rank, int nranks, SyncPage* const* syncs, unsigned long long timeout_ns, int ctas,
-                                     cudaStream_t stream, void* rs_out) {
+                                     cudaStream_t stream, void* rs_out, bool pipelined) {
   if (bytes % 16 != 0 || offset % 16 != 0 || ctas < 1 || ctas > kMaxDirectCtas || nranks > kMaxRanks) return cudaErrorInvalidValue;
   // reduce-scatter: every rank's slice must be the same whole number of vectors
   if (rs_out != nullptr && (bytes % (16ll * nranks) != 0 || reinterpret_cast<uintptr_t>(rs_out) % 16 != 0)) return cudaErrorInvalidValue;
   char* out = static_cast<char*>(rs_out);
   switch (dtype) {
-    case DT_F32: return twoshot_typed<float>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream, out);
-    case DT_BF16: return twoshot_typed<__nv_bfloat16>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream, out);
-    case DT_F16: return twoshot_typed<__half>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream, out);
+    case DT_F32: return twoshot_typed<float>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream, out, pipelined);
+    case DT_BF16: return twoshot_typed<__nv_bfloat16>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream, out, pipelined);
+    case DT_F16: return twoshot_typed<__half>(heap_bases, mc_base, offset, bytes, rank, nranks, syncs, timeout_ns, ctas, stream, out, pipelined);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -350,7 +350,8 @@ class Executor:
             auto_ctas = 8 if use_nvls else max(1, min(128, nbytes // (32 << 10) or 1))
             ctas = int(os.environ.get('MSCCL_TWOSHOT_CTAS', '0')) or auto_ctas
             comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base if use_nvls else 0, offset, nbytes, code, comm.rank,
-                                          comm.world, comm.dev_syncs, comm.timeout_ns, ctas, stream_h)
+                                          comm.world, comm.dev_syncs, comm.timeout_ns, ctas, stream_h,
+                                          pipelined=os.environ.get('MSCCL_TWOSHOT_PIPE', '0') == '1')
             self.launches += 1
             return tensor
         plan = self.select('allreduce', nbytes)
