@@ -372,6 +372,12 @@ PYBIND11_MODULE(_msccl_native, m) {
     check_rt(msccl::sm100::launch_gemm_rs_mxfp8(g, grid, as_stream(stream)), "launch of the fused fp8 GEMM reduce-scatter kernel");
   });
   m.def("sm_count", &msccl::sm100::sm_count);
+  // bf16 [rows, K] -> e4m3 values and packed UE8M0 scale blocks (one pass)
+  m.def("quantize_mxfp8", [](uintptr_t x, uintptr_t q, uintptr_t sf, int rows, int K, long long ldx, uintptr_t stream) {
+    check_rt(msccl::sm100::quantize_mxfp8(reinterpret_cast<const void*>(x), reinterpret_cast<void*>(q), reinterpret_cast<void*>(sf),
+                                          rows, K, ldx, as_stream(stream)),
+             "launch of the MX quantisation kernel");
+  });
   // Fused MoE: phase 0 = dispatch + grouped gate/up GEMM (SwiGLU), phase 1 = grouped down GEMM + combine.
   // geom = [rank, nranks, tokens, topk, hidden, ffn, num_experts, local_experts, cap, comm_ctas]
   // layout = [counts_off, meta_off, dispatch_off, combine_off, counts_parity, meta_parity, dispatch_parity, combine_parity]

@@ -8,56 +8,70 @@
 namespace msccl {
 namespace sm100 {
 
-// Sum of the n partial slabs of row block b (rows [b*BM, (b+1)*BM) of this rank's shard), in rank order,
-// fp32 accumulation, one rounding to bf16.  `part` of `parts` CTAs.
-template <typename Args>
-__device__ __forceinline__ void reduce_row_block(const Args& g, const char* my_slabs, size_t slab_bytes, int b, int part, int parts) {
-  constexpr int RU = 4;          // vectors per thread per pass; with 8 sources that is 32 loads in flight
-  const size_t first = static_cast<size_t>(b) * BM * g.N * 2 / 16;
-  const size_t count = static_cast<size_t>(BM) * g.N * 2 / 16;
-  const size_t stride = static_cast<size_t>(parts) * blockDim.x;
+constexpr int kReduceSlices = 8;       // a row block is reduced in this many independent pieces
+
+// Sum of the n partial slabs over 16-byte vectors [first, first + count) of this rank's shard, in rank order, fp32
+// accumulation, one rounding to bf16.  RU vectors per thread and pass: RU x n loads in flight per thread.
+template <int RU, typename Args>
+__device__ __forceinline__ void reduce_vectors(const Args& g, const char* my_slabs, size_t slab_bytes, size_t first, size_t count) {
   char* out = static_cast<char*>(g.out);
-  for (size_t i = static_cast<size_t>(part) * blockDim.x + threadIdx.x; i < count; i += stride * RU) {
-    uint4 in[RU][kFusedMaxRanks];
+  const size_t stride = blockDim.x;
+  for (size_t i = threadIdx.x; i < count; i += stride * RU) {
+    float acc[RU][8];
 #pragma unroll
-    for (int u = 0; u < RU; ++u) {
-      const size_t ii = i + u * stride;
+    for (int u = 0; u < RU; ++u)
 #pragma unroll
-      for (int s = 0; s < kFusedMaxRanks; ++s)
-        if (s < g.nranks && ii < count) in[u][s] = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + (first + ii) * 16);
+      for (int e = 0; e < 8; ++e) acc[u][e] = 0.0f;
+    for (int s = 0; s < g.nranks; ++s) {
+      uint4 in[RU];
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        const size_t ii = i + u * stride;
+        if (ii < count) in[u] = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + (first + ii) * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        const uint32_t w[4] = {in[u].x, in[u].y, in[u].z, in[u].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[u][2 * e] += __uint_as_float(w[e] << 16);
+          acc[u][2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+        }
+      }
     }
 #pragma unroll
     for (int u = 0; u < RU; ++u) {
       const size_t ii = i + u * stride;
-      if (ii >= count) break;
-      float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll
-      for (int s = 0; s < kFusedMaxRanks; ++s) {
-        if (s < g.nranks) {
-          const uint32_t w[4] = {in[u][s].x, in[u][s].y, in[u][s].z, in[u][s].w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            acc8[2 * e] += __uint_as_float(w[e] << 16);
-            acc8[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-          }
-        }
-      }
-      *reinterpret_cast<uint4*>(out + (first + ii) * 16) =
-          make_uint4(pack_bf16(acc8[0], acc8[1]), pack_bf16(acc8[2], acc8[3]), pack_bf16(acc8[4], acc8[5]), pack_bf16(acc8[6], acc8[7]));
+      if (ii < count)
+        *reinterpret_cast<uint4*>(out + (first + ii) * 16) =
+            make_uint4(pack_bf16(acc[u][0], acc[u][1]), pack_bf16(acc[u][2], acc[u][3]), pack_bf16(acc[u][4], acc[u][5]),
+                       pack_bf16(acc[u][6], acc[u][7]));
     }
   }
 }
 
-// Body of a reducer CTA: the rank's row blocks in the order they become complete.  `per_block` counts every source
+// Reduction work of one launch: items (row block, slice) handed out through a counter in the rank's flag page, the
+// row blocks in the order they become complete.  The dedicated reducer CTAs pull items from the start; the GEMM CTAs
+// join once their tiles are done, so the tail of the reduction has the whole GPU.  `per_block` counts every source
 // adds per (source, row block) and launch.
 template <typename Args>
-__device__ __forceinline__ void reducer_cta(const Args& g, FusedPage* page, const char* my_slabs, size_t slab_bytes,
-                                            int blocks_per_rank, unsigned long long per_block, int part, int parts) {
+__device__ __forceinline__ void reduce_items(const Args& g, FusedPage* page, const char* my_slabs, size_t slab_bytes,
+                                             int blocks_per_rank, unsigned long long per_block) {
+  __shared__ int s_item;
   __shared__ int s_ok;
-  for (int i = 0; i < blocks_per_rank; ++i) {
-    const int b = g.reduce_order[i];
-    if (threadIdx.x == 0) s_ok = 1;
+  const int total = blocks_per_rank * kReduceSlices;
+  const size_t block_vectors = static_cast<size_t>(BM) * g.N * 2 / 16;
+  const size_t slice_vectors = (block_vectors + kReduceSlices - 1) / kReduceSlices;
+  while (true) {
     __syncthreads();
+    if (threadIdx.x == 0) {
+      s_item = static_cast<int>(atomicAdd(&page->rs_work, 1u));
+      s_ok = 1;
+    }
+    __syncthreads();
+    const int item = s_item;
+    if (item >= total) break;
+    const int b = g.reduce_order[item / kReduceSlices], slice = item % kReduceSlices;
     if (static_cast<int>(threadIdx.x) < g.nranks) {
       volatile int never = 0;
       if (!wait_flag_ge(&page->rs_count[threadIdx.x][b], page->rs_base[threadIdx.x][b] + per_block, &never)) {
@@ -71,7 +85,13 @@ __device__ __forceinline__ void reducer_cta(const Args& g, FusedPage* page, cons
     }
     __syncthreads();
     if (s_ok == 0) break;
-    reduce_row_block(g, my_slabs, slab_bytes, b, part, parts);
+    const size_t begin = min(block_vectors, slice_vectors * slice);
+    const size_t count = min(block_vectors, begin + slice_vectors) - begin;
+    const size_t first = static_cast<size_t>(b) * block_vectors + begin;
+    // keep about 16 loads per thread in flight whatever the number of ranks
+    if (g.nranks <= 2) reduce_vectors<8>(g, my_slabs, slab_bytes, first, count);
+    else if (g.nranks <= 4) reduce_vectors<4>(g, my_slabs, slab_bytes, first, count);
+    else reduce_vectors<2>(g, my_slabs, slab_bytes, first, count);
   }
 }
 
@@ -87,6 +107,7 @@ __device__ __forceinline__ void finish_rs_launch(const Args& g, FusedPage* page,
       for (int s = 0; s < g.nranks; ++s)
         for (int b = 0; b < blocks_per_rank; ++b) page->rs_base[s][b] += per_block;
       page->rs_done = 0;
+      page->rs_work = 0;
       page->rs_epoch = epoch;
     }
   }

@@ -285,7 +285,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (cta >= ctas) {
     // ------------------------------------------------------------------ reducer CTAs
-    reducer_cta(g, page, g.heap_bases[g.rank] + parity_off, slab_bytes, blocks_per_rank, per_block, cta - ctas, g.reduce_ctas);
+    reduce_items(g, page, g.heap_bases[g.rank] + parity_off, slab_bytes, blocks_per_rank, per_block);
   } else {
     // ------------------------------------------------------------------ GEMM CTAs
     const Pipe p = carve_smem<3>(smem_raw);
@@ -382,6 +382,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_after_sync();
       tmem_dealloc(tmem_base, kTmemCols);
     }
+    // the tiles of this CTA are out: help with the reduction
+    reduce_items(g, page, g.heap_bases[g.rank] + parity_off, slab_bytes, blocks_per_rank, per_block);
   }
 
   finish_rs_launch(g, page, blocks_per_rank, per_block, epoch);

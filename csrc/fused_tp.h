@@ -18,6 +18,7 @@ struct alignas(128) FusedPage {
   unsigned long long ag_epoch, rs_epoch;                           // local: launches completed
   unsigned int ag_block_count[kFusedMaxBlocks];                    // local: comm CTAs done with a block
   unsigned int ag_done, rs_done;                                   // local: CTAs of the running launch that finished
+  unsigned int rs_work, rs_pad;                                    // local: reduction items of the running launch handed out
   // MoE dispatch / combine
   unsigned long long moe_flag[kFusedMaxRanks][4];
   unsigned long long moe_count[kFusedMaxRanks];                    // [source] += 1 per combine row group stored

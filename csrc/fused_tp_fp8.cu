@@ -346,7 +346,7 @@ gemm_rs_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const unsigned long long per_block = 4ull * static_cast<unsigned long long>(tiles_n);   // counts per (source, row block) and launch
 
   if (cta >= ctas) {
-    reducer_cta(g, page, g.heap_bases[g.rank] + parity_off, slab_bytes, blocks_per_rank, per_block, cta - ctas, g.reduce_ctas);
+    reduce_items(g, page, g.heap_bases[g.rank] + parity_off, slab_bytes, blocks_per_rank, per_block);
   } else {
     const F8Pipe p = carve_f8<kRsF8Stages>(smem_raw);
     const int my_tiles = (num_tiles - cta + ctas - 1) / ctas;
@@ -454,6 +454,8 @@ gemm_rs_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       tc_fence_after_sync();
       tmem_dealloc(tmem_base, kF8TmemCols);
     }
+    // the tiles of this CTA are out: help with the reduction
+    reduce_items(g, page, g.heap_bases[g.rank] + parity_off, slab_bytes, blocks_per_rank, per_block);
   }
   finish_rs_launch(g, page, blocks_per_rank, per_block, epoch);
 }

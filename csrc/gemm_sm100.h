@@ -12,6 +12,8 @@ CUtensorMap make_bf16_kmajor_map(const void* base, uint64_t rows, uint64_t cols,
 CUtensorMap make_u8_kmajor_map(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows);
 CUtensorMap make_block512_map(const void* base, uint64_t blocks);
 int sm_count();
+// bf16 [rows, K] -> e4m3 values + packed UE8M0 scale blocks (quantize_mx.cu)
+cudaError_t quantize_mxfp8(const void* x, void* q, void* sf, int rows, int K, long long ldx, cudaStream_t stream);
 // epilogue: 0 = plain bf16 store, 1 = SwiGLU over (gate | up) column halves of each tile.
 cudaError_t gemm_bf16(const void* a, const void* b, void* d, int M, int N, int K, int lda, int ldb, int ldd, int epilogue,
                       int bn, int* error_words, int max_ctas, cudaStream_t stream);

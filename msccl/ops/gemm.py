@@ -96,6 +96,26 @@ def quantize_mxfp8(x):
     return q, (exp + 127).to(torch.uint8)
 
 
+def quantize_mxfp8_packed(x, out=None, scales_out=None, stream=None):
+    """One-pass CUDA quantisation of a bf16 ``x`` [R, K] (K % 128 == 0): returns ``(q, packed_scales)`` - e4m3 values and
+    the UE8M0 scales already in the ``pack_mx_scales(..., row_multiple=128)`` arrangement (rows padded with scale 1.0).
+    Same scale rule as ``quantize_mxfp8``."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    r, k = x.shape
+    if k % 128:
+        raise ValueError(f'K must be a multiple of 128 (got {k})')
+    tiles = -(-r // 128)
+    if out is None:
+        out = torch.empty(r, k, dtype=torch.float8_e4m3fn, device=x.device)
+    if scales_out is None:
+        scales_out = (torch.empty if r % 128 == 0 else (lambda *a, **kw: torch.full(*a, fill_value=127, **kw)))(
+            (tiles * (k // 128) * 512,), dtype=torch.uint8, device=x.device)
+    assert out.is_contiguous() and scales_out.numel() == tiles * (k // 128) * 512
+    stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+    load().quantize_mxfp8(x.data_ptr(), out.data_ptr(), scales_out.data_ptr(), r, k, x.stride(0), stream_h)
+    return out, scales_out
+
+
 def dequantize_mxfp8(q, scales):
     """fp32 values of a ``quantize_mxfp8`` pair."""
     r, k = q.shape

@@ -10,7 +10,7 @@ SwiGLU output before the down projection); accumulation is fp32 and the result b
 import torch
 
 from msccl.ops.fused_tp import FusedTensorParallel
-from msccl.ops.gemm import interleave_gate_up, pack_mx_scales, quantize_mxfp8
+from msccl.ops.gemm import interleave_gate_up, pack_mx_scales, quantize_mxfp8, quantize_mxfp8_packed
 
 
 class TensorParallelMLP:
@@ -41,12 +41,10 @@ class TensorParallelMLP:
     def forward(self, x_local, out=None):
         """x_local: [tokens_per_rank, hidden] -> this rank's [tokens_per_rank, hidden] of the MLP output."""
         if self.precision == 'mxfp8':
-            xq, sx = quantize_mxfp8(x_local)
-            self.fused.all_gather_gemm_mxfp8(xq, pack_mx_scales(sx, row_multiple=128), self.wq_gate_up, self.sf_gate_up,
-                                             epilogue='swiglu', out=self.h)
-            hq, sh = quantize_mxfp8(self.h)
-            return self.fused.gemm_reduce_scatter_mxfp8(hq, pack_mx_scales(sh, row_multiple=128), self.wq_down, self.sf_down,
-                                                        out=out)
+            xq, sx = quantize_mxfp8_packed(x_local)                  # one kernel each: values + packed scales
+            self.fused.all_gather_gemm_mxfp8(xq, sx, self.wq_gate_up, self.sf_gate_up, epilogue='swiglu', out=self.h)
+            hq, sh = quantize_mxfp8_packed(self.h)
+            return self.fused.gemm_reduce_scatter_mxfp8(hq, sh, self.wq_down, self.sf_down, out=out)
         self.fused.all_gather_gemm(x_local, self.w_gate_up, epilogue='swiglu', out=self.h)
         return self.fused.gemm_reduce_scatter(self.h, self.w_down, out=out)
 

@@ -123,7 +123,8 @@ class Communicator:
             # largest block of the one-shot LL kernels.  Measured: with 8 ranks blocks of 128 KB still beat the
             # barrier-based kernels and NCCL (17 us against 27 us for a 1 MB all-gather), blocks of 512 KB do
             # not (38 us against 28-30 us); with 2 ranks 1 MB blocks do (12.5 us against 17 us).
-            ll_max_bytes = max(256 << 10, (2 << 20) // self.world)
+            # (2 ranks: 2 MB blocks; measured 27 us for the barrier-based kernels on 2 MB blocks against 24 us for NCCL)
+            ll_max_bytes = (2 << 20) if self.world == 2 else max(256 << 10, (2 << 20) // self.world)
         self._set_layout(self.world, ll_max_bytes, fifo_bytes, arena_bytes)
         mode = mode or os.environ.get('MSCCL_SYMM', 'auto')
         errors = []

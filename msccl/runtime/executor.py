@@ -293,7 +293,7 @@ class Executor:
         nat = comm.native
         if plan.nvls_kind == 'allreduce':
             nat.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, offset, nbytes, code, rank, world, comm.dev_syncs,
-                                  comm.timeout_ns, 8, stream_h)
+                                  comm.timeout_ns, 8, stream_h, pipelined=os.environ.get('MSCCL_TWOSHOT_PIPE', '0') == '1')
             result = t_in
         elif plan.nvls_kind == 'allgather':            # in place: the own block already sits at its position
             block = nbytes // world

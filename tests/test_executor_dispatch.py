@@ -33,7 +33,7 @@ class FakeComm:
         self.local_ranks = [rank]
         self.native = FakeNative()
         self.mc_base = 5000 if multicast else 0
-        self.ll_max_bytes = max(256 << 10, (2 << 20) // world)
+        self.ll_max_bytes = (2 << 20) if world == 2 else max(256 << 10, (2 << 20) // world)
         self.ll_slot_bytes = 2 * self.ll_max_bytes
         self.arena = torch.zeros(64 << 20, dtype=torch.uint8)
 
@@ -138,7 +138,7 @@ def test_in_switch_programs_go_to_the_native_kernels(ex):
 def test_two_ranks_prefer_peer_loads_and_large_one_shot_blocks():
     ex = Executor(FakeComm(world=2, rank=1))
     s = FakeStream()
-    assert ex.comm.ll_max_bytes == 1 << 20
+    assert ex.comm.ll_max_bytes == 2 << 20
     t = ex.comm.symmetric(8 << 20, torch.bfloat16)
     ex.all_reduce(t, stream=s)
     assert last(ex)[0] == 'twoshot_allreduce' and last(ex)[1][1] == 0            # peer loads in rank order on 2 GPUs

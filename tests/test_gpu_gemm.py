@@ -125,3 +125,21 @@ def test_gemm_cta_pair_identity_and_swiglu():
     h = gemm_bf16(x, w, epilogue='swiglu', pair=True)
     check_gemm_errors()
     assert torch.equal(h, gemm_bf16(x, w, epilogue='swiglu', pair=False))
+
+
+def test_one_pass_mx_quantisation_matches_the_torch_reference():
+    """``quantize_mxfp8_packed`` (one CUDA kernel: e4m3 values + packed scale blocks) against ``quantize_mxfp8`` +
+    ``pack_mx_scales`` written in torch: the same scale rule, so the bytes agree (a handful of groups whose largest
+    magnitude sits exactly on a power-of-two boundary may round the other way in torch's float log2)."""
+    from msccl.ops.gemm import pack_mx_scales, quantize_mxfp8, quantize_mxfp8_packed
+    gen = torch.Generator(device='cuda').manual_seed(3)
+    for rows, k in ((256, 512), (200, 1024), (1024, 1792)):
+        x = (torch.randn(rows, k, device='cuda', generator=gen) * torch.rand(rows, 1, device='cuda', generator=gen) * 4).bfloat16()
+        x[3, :64] = 0                                   # an all-zero group
+        q, packed = quantize_mxfp8_packed(x)
+        q_ref, s_ref = quantize_mxfp8(x.float())
+        packed_ref = pack_mx_scales(s_ref, row_multiple=128)
+        assert packed.shape == packed_ref.shape
+        same_scale = (packed == packed_ref).float().mean().item()
+        same_value = (q.view(torch.uint8) == q_ref.view(torch.uint8)).float().mean().item()
+        assert same_scale > 0.999 and same_value > 0.995, (rows, k, same_scale, same_value)
