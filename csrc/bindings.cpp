@@ -278,7 +278,7 @@ PYBIND11_MODULE(_msccl_native, m) {
   m.def("ag_gemm", [](uintptr_t x_local, uintptr_t b, uintptr_t d, int rows_per_rank, int N, int K, int ldb, int ldd, int rank,
                        int nranks, int comm_ctas, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs, size_t off_fused,
                        uintptr_t mc_base, size_t gathered_off, size_t gathered_bytes, uintptr_t error_words, int epilogue,
-                       int grid, int tuning, uintptr_t order, uintptr_t stream) {
+                       int grid, int tuning, uintptr_t order, uintptr_t stream, bool pair) {
     msccl::sm100::AgGemmArgs g;
     std::memset(&g, 0, sizeof(g));
     g.x_local = reinterpret_cast<const void*>(x_local);
@@ -297,13 +297,17 @@ PYBIND11_MODULE(_msccl_native, m) {
     g.gathered_off = gathered_off;
     g.gathered_bytes = gathered_bytes;
     g.error_words = reinterpret_cast<int*>(error_words);
-    check_rt(msccl::sm100::launch_ag_gemm(g, epilogue, grid, as_stream(stream)), "launch of the fused all-gather GEMM kernel");
-  });
+    if (pair) check_rt(msccl::sm100::launch_ag_gemm_2cta(g, epilogue, grid, as_stream(stream)), "launch of the fused all-gather GEMM kernel (CTA pairs)");
+    else check_rt(msccl::sm100::launch_ag_gemm(g, epilogue, grid, as_stream(stream)), "launch of the fused all-gather GEMM kernel");
+  }, py::arg("x_local"), py::arg("b"), py::arg("d"), py::arg("rows_per_rank"), py::arg("N"), py::arg("K"), py::arg("ldb"), py::arg("ldd"),
+     py::arg("rank"), py::arg("nranks"), py::arg("comm_ctas"), py::arg("heap_bases_dev"), py::arg("heap_ptrs"), py::arg("off_fused"),
+     py::arg("mc_base"), py::arg("gathered_off"), py::arg("gathered_bytes"), py::arg("error_words"), py::arg("epilogue"), py::arg("grid"),
+     py::arg("tuning"), py::arg("order"), py::arg("stream"), py::arg("pair") = false);
   // Fused GEMM -> reduce-scatter.
   m.def("gemm_rs", [](uintptr_t a, uintptr_t b, uintptr_t out, int rows_per_rank, int N, int K, int lda, int ldb, int rank,
                        int nranks, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs, size_t off_fused, size_t partial_off,
                        uintptr_t error_words, int grid, uintptr_t order, uintptr_t reduce_order, int reduce_ctas,
-                       uintptr_t stream) {
+                       uintptr_t stream, bool pair) {
     msccl::sm100::GemmRsArgs g;
     std::memset(&g, 0, sizeof(g));
     g.a = reinterpret_cast<const void*>(a);
@@ -319,8 +323,12 @@ PYBIND11_MODULE(_msccl_native, m) {
     g.order = reinterpret_cast<const int*>(order);
     g.reduce_order = reinterpret_cast<const int*>(reduce_order);
     g.reduce_ctas = reduce_ctas;
-    check_rt(msccl::sm100::launch_gemm_rs(g, grid, as_stream(stream)), "launch of the fused GEMM reduce-scatter kernel");
-  });
+    if (pair) check_rt(msccl::sm100::launch_gemm_rs_2cta(g, grid, as_stream(stream)), "launch of the fused GEMM reduce-scatter kernel (CTA pairs)");
+    else check_rt(msccl::sm100::launch_gemm_rs(g, grid, as_stream(stream)), "launch of the fused GEMM reduce-scatter kernel");
+  }, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("rows_per_rank"), py::arg("N"), py::arg("K"), py::arg("lda"), py::arg("ldb"),
+     py::arg("rank"), py::arg("nranks"), py::arg("heap_bases_dev"), py::arg("heap_ptrs"), py::arg("off_fused"), py::arg("partial_off"),
+     py::arg("error_words"), py::arg("grid"), py::arg("order"), py::arg("reduce_order"), py::arg("reduce_ctas"), py::arg("stream"),
+     py::arg("pair") = false);
   // The same two kernels on block-scaled fp8 operands (e4m3 values + packed UE8M0 scale blocks).
   m.def("ag_gemm_mxfp8", [](uintptr_t x_local, uintptr_t sf_local, uintptr_t b, uintptr_t sfb, uintptr_t d, int rows_per_rank, int N,
                              int K, int ldb, int ldd, int rank, int nranks, int comm_ctas, uintptr_t heap_bases_dev,

@@ -99,6 +99,9 @@ struct GemmRsF8Args {
 };
 
 cudaError_t launch_ag_gemm(const AgGemmArgs& args, int epilogue, int grid, cudaStream_t stream);
+// the same two kernels on CTA pairs (cta_group::2, 256 x 256 tiles; fused_tp_2cta.cu)
+cudaError_t launch_ag_gemm_2cta(const AgGemmArgs& args, int epilogue, int grid, cudaStream_t stream);
+cudaError_t launch_gemm_rs_2cta(const GemmRsArgs& args, int grid, cudaStream_t stream);
 cudaError_t launch_ag_gemm_mxfp8(const AgGemmF8Args& args, int epilogue, int grid, cudaStream_t stream);
 cudaError_t launch_gemm_rs_mxfp8(const GemmRsF8Args& args, int grid, cudaStream_t stream);
 cudaError_t launch_gemm_rs(const GemmRsArgs& args, int grid, cudaStream_t stream);

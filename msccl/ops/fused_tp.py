@@ -40,6 +40,9 @@ class FusedTensorParallel:
         self.tuning = int(os.environ.get('MSCCL_AG_TUNING', '0'))
         self.grid = int(os.environ.get('MSCCL_AG_GRID', '0'))
         self.reduce_ctas = int(os.environ.get('MSCCL_RS_REDUCE_CTAS', '12'))
+        # CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles) whenever the row blocks pair up; MSCCL_FUSED_PAIR=0: single CTAs
+        self.pair = (os.environ.get('MSCCL_FUSED_PAIR', '1') != '0' and (self.n * (tokens_per_rank // 128)) % 2 == 0
+                     and self.comm_ctas % 2 == 0 and self.reduce_ctas % 2 == 0)
         self.set_schedule()
 
     def set_schedule(self, ag_channels=1, rs_channels=1):
@@ -66,7 +69,8 @@ class FusedTensorParallel:
         c.native.ag_gemm(x_local.data_ptr(), weight.data_ptr(), out.data_ptr(), self.rows, n_out, k, weight.stride(0),
                          out.stride(0), c.rank, self.n, self.comm_ctas, c.dev_heap_bases, list(c.heap_ptrs), c.off_fused,
                          c.mc_base, self.gathered_off, self.gathered_bytes, _errors(x_local.device).data_ptr(),
-                         1 if swiglu else 0, self.grid or self.sms, self.tuning, self.ag_order.data_ptr(), stream_h)
+                         1 if swiglu else 0, self.grid or (0 if self.pair else self.sms), self.tuning, self.ag_order.data_ptr(),
+                         stream_h, pair=self.pair)
         self.launches += 1
         return out
 
@@ -82,8 +86,8 @@ class FusedTensorParallel:
         stream_h = (stream or torch.cuda.current_stream()).cuda_stream
         c.native.gemm_rs(a.data_ptr(), weight.data_ptr(), out.data_ptr(), self.rows, self.hidden, k, a.stride(0),
                          weight.stride(0), c.rank, self.n, c.dev_heap_bases, list(c.heap_ptrs), c.off_fused, self.partial_off,
-                         _errors(a.device).data_ptr(), self.sms, self.rs_order.data_ptr(), self.reduce_order.data_ptr(),
-                         min(self.reduce_ctas, self.sms - 1), stream_h)
+                         _errors(a.device).data_ptr(), 0 if self.pair else self.sms, self.rs_order.data_ptr(),
+                         self.reduce_order.data_ptr(), min(self.reduce_ctas, self.sms - 1), stream_h, pair=self.pair)
         self.launches += 1
         return out
 
