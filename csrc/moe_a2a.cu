@@ -28,8 +28,11 @@ namespace {
 
 struct TileInfo { int expert, m0, tn, rows; };
 
-// Grouped tile enumeration: experts in order, row tiles of an expert, then column tiles fastest.
-// m_tiles[e] = ceil(rows_e / 128).  Returns false when `tile` is past the end.
+// Grouped tile enumeration: experts in order, column tiles of an expert, then its row tiles fastest
+// (m_tiles[e] = ceil(rows_e / 128)).  The CTAs that run side by side therefore share a handful of
+// weight tiles and read the expert's rows - a few MB - from L2: the weights of one expert (235 MB of
+// gate and up rows at hidden 4096, ffn 14336) do not fit into L2, and with the column tiles fastest
+// every row tile streamed them from DRAM again.  Returns false when `tile` is past the end.
 __device__ __forceinline__ bool decode_grouped(int tile, const int* rows_per_expert, int local_experts, int tiles_n,
                                                TileInfo& t) {
   int base = 0;
@@ -39,8 +42,8 @@ __device__ __forceinline__ bool decode_grouped(int tile, const int* rows_per_exp
     if (tile < base + here) {
       const int in_e = tile - base;
       t.expert = e;
-      t.m0 = (in_e / tiles_n) * BM;
-      t.tn = in_e % tiles_n;
+      t.m0 = (in_e % mt) * BM;
+      t.tn = in_e / mt;
       t.rows = min(BM, rows_per_expert[e] - t.m0);
       return true;
     }

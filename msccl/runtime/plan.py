@@ -340,6 +340,8 @@ def tile_geometry(plan: HostPlan, chunk_elems: int, elem_size: int, slot_bytes: 
     multiples of 16 bytes run as LL)."""
     proto = plan.proto if proto is None else proto
     per_access = width // elem_size
+    if (chunk_elems * elem_size) % width:
+        raise PlanError(f'chunks of {chunk_elems * elem_size} bytes are not whole {width}-byte accesses')
     if proto == 2:
         if width != 16:
             raise PlanError('LL128 needs chunks that are multiples of 16 bytes')

@@ -156,10 +156,10 @@ def test_compiled_plan_tables_are_consistent():
         allreduce_ring(n, 2)
     algo = load_xml(prog.generate_xml())
     plan = compile_plan(algo, list(range(n)), slot)
-    tb_fmt, step_fmt = struct.Struct('<4h4i2i2q'), struct.Struct('<4B2h3i')
-    assert tb_fmt.size == 48 and step_fmt.size == 20
-    tbs = [tb_fmt.unpack_from(plan.tb_bytes, i * 48) for i in range(len(plan.tb_bytes) // 48)]
-    steps = [step_fmt.unpack_from(plan.step_bytes, i * 20) for i in range(len(plan.step_bytes) // 20)]
+    tb_fmt, step_fmt = struct.Struct('<4h4i2i2q4i'), struct.Struct('<4B2h3i4Bi2H')       # DevTb, DevStep of the kernel
+    assert tb_fmt.size == 64 and step_fmt.size == 32
+    tbs = [tb_fmt.unpack_from(plan.tb_bytes, i * 64)[:12] for i in range(len(plan.tb_bytes) // 64)]
+    steps = [step_fmt.unpack_from(plan.step_bytes, i * 32)[:9] for i in range(len(plan.step_bytes) // 32)]
     assert len(tbs) == algo.num_threadblocks() == plan.total_tbs() and len(steps) == algo.num_steps()
     send_off, recv_off = {}, {}
     for rank, tb_id, send_peer, recv_peer, chan, nsteps, first, tbs_in_rank, send_conn, recv_conn, s_off, r_off in tbs:
