@@ -392,7 +392,7 @@ PYBIND11_MODULE(_msccl_native, m) {
   m.def("moe_phase", [](int phase, std::vector<int> geom, std::vector<size_t> layout, uintptr_t heap_bases_dev,
                          std::vector<uintptr_t> heap_ptrs, size_t off_fused, size_t moe_off, uintptr_t x, uintptr_t sorted_copy,
                          uintptr_t expert_start, uintptr_t copy_weight, uintptr_t w_gate_up, uintptr_t h, uintptr_t w_down,
-                         uintptr_t y, uintptr_t error_words, int grid, uintptr_t stream) {
+                         uintptr_t y, uintptr_t error_words, int grid, uintptr_t stream, bool pair) {
     if (geom.size() != 10 || layout.size() != 8) throw std::runtime_error("bad geometry/layout vectors");
     msccl::sm100::MoeArgs g;
     std::memset(&g, 0, sizeof(g));
@@ -416,8 +416,24 @@ PYBIND11_MODULE(_msccl_native, m) {
     g.w_down = reinterpret_cast<const void*>(w_down);
     g.y = reinterpret_cast<void*>(y);
     g.error_words = reinterpret_cast<int*>(error_words);
-    if (phase == 0) check_rt(msccl::sm100::launch_moe_dispatch_gemm(g, grid, as_stream(stream)), "launch of the MoE dispatch kernel");
-    else check_rt(msccl::sm100::launch_moe_gemm_combine(g, grid, as_stream(stream)), "launch of the MoE combine kernel");
+    if (pair) {
+      if (phase == 0) check_rt(msccl::sm100::launch_moe_dispatch_gemm_2cta(g, grid, as_stream(stream)), "launch of the MoE dispatch kernel (pairs)");
+      else check_rt(msccl::sm100::launch_moe_gemm_combine_2cta(g, grid, as_stream(stream)), "launch of the MoE combine kernel (pairs)");
+    } else {
+      if (phase == 0) check_rt(msccl::sm100::launch_moe_dispatch_gemm(g, grid, as_stream(stream)), "launch of the MoE dispatch kernel");
+      else check_rt(msccl::sm100::launch_moe_gemm_combine(g, grid, as_stream(stream)), "launch of the MoE combine kernel");
+    }
+  }, py::arg("phase"), py::arg("geom"), py::arg("layout"), py::arg("heap_bases_dev"), py::arg("heap_ptrs"), py::arg("off_fused"),
+     py::arg("moe_off"), py::arg("x"), py::arg("sorted_copy"), py::arg("expert_start"), py::arg("copy_weight"), py::arg("w_gate_up"),
+     py::arg("h"), py::arg("w_down"), py::arg("y"), py::arg("error_words"), py::arg("grid"), py::arg("stream"), py::arg("pair") = false);
+  // MoE routing on the device: top-k of the gate logits, and the stable sort of the token copies by expert.
+  m.def("moe_topk", [](uintptr_t logits, int tokens, int experts, int k, uintptr_t out_experts, uintptr_t out_weights, uintptr_t stream) {
+    check_rt(msccl::sm100::launch_moe_topk(reinterpret_cast<const float*>(logits), tokens, experts, k, reinterpret_cast<int*>(out_experts),
+                                           reinterpret_cast<float*>(out_weights), as_stream(stream)), "launch of the MoE top-k kernel");
+  });
+  m.def("moe_sort", [](uintptr_t expert_of, int n, int experts, uintptr_t sorted_copy, uintptr_t expert_start, uintptr_t stream) {
+    check_rt(msccl::sm100::launch_moe_sort(reinterpret_cast<const int*>(expert_of), n, experts, reinterpret_cast<int*>(sorted_copy),
+                                           reinterpret_cast<int*>(expert_start), as_stream(stream)), "launch of the MoE sort kernel");
   });
   // In-place all-reduce of `bytes` at `offset` of every rank's symmetric heap.  mc_base = 0
   // selects peer loads/stores, otherwise the NVLink multicast window is used.

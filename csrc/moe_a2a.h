@@ -46,6 +46,16 @@ struct MoeArgs {
 
 cudaError_t launch_moe_dispatch_gemm(const MoeArgs& args, int grid, cudaStream_t stream);
 cudaError_t launch_moe_gemm_combine(const MoeArgs& args, int grid, cudaStream_t stream);
+// The same two kernels on CTA pairs (moe_a2a_2cta.cu): comm_ctas must be even; grid 0 = all resident pairs.
+cudaError_t launch_moe_dispatch_gemm_2cta(const MoeArgs& args, int grid, cudaStream_t stream);
+cudaError_t launch_moe_gemm_combine_2cta(const MoeArgs& args, int grid, cudaStream_t stream);
+
+// Routing on the device (moe_route.cu).  launch_moe_topk: logits [tokens, experts] fp32 -> the k largest experts of
+// every token (int32, descending) and their renormalised softmax weights.  launch_moe_sort: stable counting sort of
+// the n = tokens * k copies by expert -> sorted_copy [n] and expert_start [experts + 1].
+cudaError_t launch_moe_topk(const float* logits, int tokens, int experts, int k, int* out_experts, float* out_weights,
+                            cudaStream_t stream);
+cudaError_t launch_moe_sort(const int* expert_of, int n, int experts, int* sorted_copy, int* expert_start, cudaStream_t stream);
 
 }  // namespace sm100
 }  // namespace msccl

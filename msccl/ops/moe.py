@@ -36,6 +36,8 @@ class FusedMoE:
         expected = n * tokens * topk / num_experts
         self.cap = _align(int(expected * capacity_factor) + 128, 128)
         self.comm_ctas = int(os.environ.get('MSCCL_COMM_CTAS', comm_ctas))
+        # CTA pairs (cta_group::2) by default; MSCCL_MOE_PAIR=0 selects the single-CTA kernels
+        self.pair = os.environ.get('MSCCL_MOE_PAIR', '1') != '0' and self.comm_ctas % 2 == 0 and hidden % 256 == 0
         le, cap = self.local_experts, self.cap
         counts_p = _align(n * num_experts * 4, 256)
         meta_p = _align(le * cap * 16, 256)
@@ -48,6 +50,22 @@ class FusedMoE:
         self.h = torch.empty(le * cap, ffn, dtype=torch.bfloat16, device=f'cuda:{comm.device}')
         self.sms = comm.native.sm_count()
         self.launches = 0
+        dev = f'cuda:{comm.device}'
+        self._sorted = torch.empty(tokens * topk, dtype=torch.int32, device=dev)
+        self._start = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+        self._route_e = torch.empty(tokens, topk, dtype=torch.int32, device=dev)
+        self._route_w = torch.empty(tokens, topk, dtype=torch.float32, device=dev)
+
+    def route(self, gate_logits, stream=None):
+        """``route_top_k`` in one kernel of this package: gate logits [tokens, num_experts] -> (expert ids [tokens, k]
+        int32, weights [tokens, k] fp32).  The tensors returned are reused by the next call."""
+        assert gate_logits.shape == (self.tokens, self.num_experts)
+        logits = gate_logits.float().contiguous()
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        self.comm.native.moe_topk(logits.data_ptr(), self.tokens, self.num_experts, self.topk, self._route_e.data_ptr(),
+                                  self._route_w.data_ptr(), stream_h)
+        self.launches += 1
+        return self._route_e, self._route_w
 
     def pack_weights(self, w_gate, w_up, w_down):
         """w_gate / w_up: [local_experts, ffn, hidden]; w_down: [local_experts, hidden, ffn] -> the stacked
@@ -59,22 +77,22 @@ class FusedMoE:
         """x [tokens, hidden] bf16; experts/weights [tokens, topk] from ``route_top_k``.  Returns y [tokens, hidden]."""
         c = self.comm
         assert x.shape == (self.tokens, self.hidden) and x.is_contiguous() and x.dtype == torch.bfloat16
-        flat = experts.reshape(-1)
-        sorted_copy = torch.argsort(flat, stable=True).to(torch.int32)
-        counts = torch.bincount(flat, minlength=self.num_experts)
-        expert_start = torch.zeros(self.num_experts + 1, dtype=torch.int32, device=x.device)
-        expert_start[1:] = torch.cumsum(counts, 0).to(torch.int32)
+        assert experts.shape == (self.tokens, self.topk) and weights.shape == (self.tokens, self.topk)
+        flat = experts.reshape(-1).to(torch.int32).contiguous()
         copy_weight = weights.reshape(-1).float().contiguous()
         if out is None:
             out = torch.empty_like(x)
+        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        # stable counting sort of the copies by expert: the order and the per-expert prefix the dispatch kernel reads
+        sorted_copy, expert_start = self._sorted, self._start
+        c.native.moe_sort(flat.data_ptr(), flat.numel(), self.num_experts, sorted_copy.data_ptr(), expert_start.data_ptr(), stream_h)
         geom = [c.rank, self.n, self.tokens, self.topk, self.hidden, self.ffn, self.num_experts, self.local_experts,
                 self.cap, self.comm_ctas]
-        stream_h = (stream or torch.cuda.current_stream()).cuda_stream
         args = (geom, self.layout, c.dev_heap_bases, list(c.heap_ptrs), c.off_fused, self.moe_off, x.data_ptr(),
                 sorted_copy.data_ptr(), expert_start.data_ptr(), copy_weight.data_ptr(), w_gate_up.data_ptr(),
                 self.h.data_ptr(), w_down.data_ptr(), out.data_ptr(), _errors(x.device).data_ptr(), self.sms, stream_h)
-        c.native.moe_phase(0, *args)
-        c.native.moe_phase(1, *args)
-        self.launches += 2
-        self._keep = (sorted_copy, expert_start, copy_weight)      # alive until the kernels have run
+        c.native.moe_phase(0, *args, self.pair)
+        c.native.moe_phase(1, *args, self.pair)
+        self.launches += 3
+        self._keep = (flat, copy_weight)                           # alive until the kernels have run
         return out

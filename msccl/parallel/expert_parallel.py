@@ -1,7 +1,7 @@
 """Expert-parallel MoE layer: top-k routing, fused dispatch + expert FFN + combine."""
 import torch
 
-from msccl.ops.moe import FusedMoE, route_top_k
+from msccl.ops.moe import FusedMoE
 
 
 class ExpertParallelMoE:
@@ -20,7 +20,7 @@ class ExpertParallelMoE:
     def forward(self, x, gate_logits=None, out=None):
         if gate_logits is None:
             gate_logits = x @ self.w_router.t()
-        experts, weights = route_top_k(gate_logits, self.topk)
+        experts, weights = self.moe.route(gate_logits)       # top-k of the softmax, renormalised (route_top_k in one kernel)
         return self.moe.forward(x, experts, weights, self.w_gate_up, self.w_down, out=out)
 
     __call__ = forward

@@ -42,9 +42,11 @@ def make_weights(le, ffn, hidden, seed):
     return wg, wu, wd
 
 
-def check(comm, rank, n, tokens=256, hidden=512, ffn=512, le=2, calls=3):
+def check(comm, rank, n, tokens=256, hidden=512, ffn=512, le=2, calls=3, pair=True):
     num_experts = le * n
     moe = FusedMoE(comm, tokens, hidden, ffn, num_experts, topk=2, capacity_factor=3.0, comm_ctas=4)
+    assert moe.pair, 'CTA pairs are the default'
+    moe.pair = pair
     wg, wu, wd = make_weights(le, ffn, hidden, 10 + rank)
     wgu, wdn = moe.pack_weights(wg, wu, wd)
     all_wg = [torch.empty_like(wg) for _ in range(n)]
@@ -57,8 +59,21 @@ def check(comm, rank, n, tokens=256, hidden=512, ffn=512, le=2, calls=3):
         x = torch.randn(tokens, hidden, device='cuda', generator=gen).bfloat16()
         logits = torch.randn(tokens, num_experts, device='cuda', generator=gen)
         experts, weights = route_top_k(logits, 2)
-        y = moe.forward(x, experts, weights, wgu, wdn)
+        if call % 2 == 0:
+            # routing in this package's own kernel: the same experts in the same order, the same weights
+            dev_experts, dev_weights = moe.route(logits)
+            assert torch.equal(dev_experts.long(), experts), ('route ids', call)
+            assert (dev_weights - weights).abs().max().item() < 1e-5, ('route weights', call)
+            y = moe.forward(x, dev_experts, dev_weights, wgu, wdn)
+        else:
+            y = moe.forward(x, experts, weights, wgu, wdn)
         check_gemm_errors()
+        # the sort the dispatch kernel read: stable by expert
+        flat = experts.reshape(-1)
+        assert torch.equal(moe._sorted.long(), torch.argsort(flat, stable=True)), ('sorted copies', call)
+        start = torch.zeros(num_experts + 1, dtype=torch.long, device='cuda')
+        start[1:] = torch.cumsum(torch.bincount(flat, minlength=num_experts), 0)
+        assert torch.equal(moe._start.long(), start), ('expert prefix', call)
         want = torch.zeros(tokens, hidden, device='cuda')
         xf = x.float()
         for e in range(num_experts):
@@ -147,6 +162,8 @@ def main():
     rank, n = dist.get_rank(), dist.get_world_size()
     comm = Communicator.from_process_group(fifo_bytes=16 << 20, arena_bytes=(1024 << 20) if args.bench else (64 << 20))
     check(comm, rank, n)
+    check(comm, rank, n, tokens=320, calls=2)                  # an odd number of row tiles per expert: half-empty pairs
+    check(comm, rank, n, pair=False, calls=2)                  # the single-CTA kernels
     if rank == 0:
         print('FUSED_MOE_OK', flush=True)
     if args.bench:
