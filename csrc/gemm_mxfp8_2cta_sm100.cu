@@ -11,8 +11,9 @@
 //   per 128-byte K block, all as tensor loads that complete on the leader's mbarrier; the leader issues tcgen05.cp.cta_group::2 (scales to tensor memory in both
 //   CTAs) and tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale (M 256, N 256, K 32).
 // Tensor memory: one 256-column accumulator plus 12 scale columns per pipeline stage.  Two accumulator
-// stages of 256 columns would fill all 512 columns, so the epilogue of a tile is not overlapped with the
-// next tile's MMAs; it costs about 1.5 us per tile against 8-17 us of MMAs for K 4096-8192.
+// stages of 256 columns would fill all 512 columns, so the epilogue of a tile cannot run beside the
+// next tile's MMAs as a whole; what is kept off the critical path is its second half: the epilogue warps
+// pack the accumulator to bf16 in shared memory, release it, and only then store to global memory.
 // Barriers and failure handling as in gemm_2cta_sm100.cu.
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -27,7 +28,7 @@ namespace sm100 {
 namespace {
 
 constexpr int QBM = 256, QBN = 256, QBK = 128;
-constexpr int kQStages = 6;
+constexpr int kQStages = 5;                        // pipeline stages; the shared memory of a sixth holds the staged epilogue
 constexpr int kQGroupM = 8;
 constexpr int kQABytes = BM * QBK;                 // 16 KB: this CTA's 128 rows of A
 constexpr int kQBBytes = (QBN / 2) * QBK;          // 16 KB: this CTA's 128 rows of B
@@ -36,8 +37,15 @@ constexpr int kQLoadBytes = kQABytes + kQBBytes + 3 * kQSfBytes;   // bytes one 
 constexpr int kQStageBytes = 34 * 1024;            // stage pitch: operand tiles stay 1024-byte aligned
 constexpr int kQTmemCols = 512;                    // [0,256) accumulator, then 12 scale columns per stage
 constexpr int kQSfTmemBase = QBN;
-constexpr size_t kQSmemBytes = 1024 + static_cast<size_t>(kQStages) * kQStageBytes + 256;
+// Staged epilogue: an epilogue warp packs its 32 rows x kQStageCols columns to bf16 in shared memory (one row per
+// lane), then stores whole row segments with consecutive lanes on consecutive 16 bytes.  After the last pass into
+// shared memory the accumulator is free for the next tile while the stores are still being issued.
+constexpr int kQStageCols = 128;
+constexpr int kQEpiPitch = kQStageCols * 2 + 16;   // bytes per staged row (16 of padding spread the banks)
+constexpr int kQEpiPerWarp = 32 * kQEpiPitch;
+constexpr size_t kQSmemBytes = 1024 + static_cast<size_t>(kQStages) * kQStageBytes + 256 + 4 * kQEpiPerWarp;
 static_assert(kQLoadBytes <= kQStageBytes, "stage pitch too small");
+static_assert(kQSmemBytes <= 227 * 1024, "shared memory of one CTA");
 
 __device__ __forceinline__ void tma_load_2d_pair8(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
   asm volatile(
@@ -83,6 +91,7 @@ gemm_mxfp8_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   uint64_t* acc_empty = bars + 2 * kQStages + 1;     // leader only: 8 epilogue warps of the pair
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kQStages + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_base = smem + static_cast<size_t>(kQStages) * kQStageBytes + 256;
 
   __shared__ int s_skip;                             // the leader's reading decides for the pair
   if (threadIdx.x == 0) s_skip = (error_words != nullptr && *reinterpret_cast<volatile int*>(error_words) != 0) ? 1 : 0;
@@ -217,27 +226,54 @@ gemm_mxfp8_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         break;
       }
       tc_fence_after_sync();
-      const int row = tm * QBM + static_cast<int>(cta_rank) * BM + quarter * 32 + lane;
+      const int row0 = tm * QBM + static_cast<int>(cta_rank) * BM + quarter * 32;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      uint8_t* epi = epi_base + (warp - 2) * kQEpiPerWarp;
+      constexpr int kLanesPerRow = kQStageCols * 2 / 16, kRowsPerStore = 32 / kLanesPerRow;
 #pragma unroll 1
-      for (int c = 0; c < QBN; c += 32) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c, r);
-        tc_wait_ld();
-        if (row < M) {
-          uint4* out = reinterpret_cast<uint4*>(d + static_cast<size_t>(row) * ldd + tn * QBN + c);
+      for (int c0 = 0; c0 < QBN; c0 += kQStageCols) {
+        // tensor memory -> registers -> shared memory; the load of the next 32 columns is in flight while these are packed
+        uint32_t r[2][32];
+        tmem_ld32(taddr + c0, r[0]);
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            out[v] = make_uint4(pack_bf16(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1])),
-                                pack_bf16(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
-                                pack_bf16(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
-                                pack_bf16(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7])));
+        for (int c = 0; c < kQStageCols; c += 32) {
+          const int cur = (c / 32) & 1;
+          tc_wait_ld();
+          if (c + 32 < kQStageCols) tmem_ld32(taddr + c0 + c + 32, r[cur ^ 1]);
+          uint4* dst = reinterpret_cast<uint4*>(epi + lane * kQEpiPitch + c * 2);
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            dst[v] = make_uint4(pack_bf16(__uint_as_float(r[cur][8 * v + 0]), __uint_as_float(r[cur][8 * v + 1])),
+                                pack_bf16(__uint_as_float(r[cur][8 * v + 2]), __uint_as_float(r[cur][8 * v + 3])),
+                                pack_bf16(__uint_as_float(r[cur][8 * v + 4]), __uint_as_float(r[cur][8 * v + 5])),
+                                pack_bf16(__uint_as_float(r[cur][8 * v + 6]), __uint_as_float(r[cur][8 * v + 7])));
+        }
+        if (c0 + kQStageCols == QBN) {
+          // the accumulator has been read completely: the MMAs of the next tile may overwrite it
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(acc_empty), 0));
+        } else {
+          __syncwarp();
+        }
+        // shared memory -> global: kRowsPerStore rows of kQStageCols bf16 per instruction, eight instructions in flight
+        const int sub_row = lane / kLanesPerRow, sub_col = (lane % kLanesPerRow) * 16;
+        __nv_bfloat16* out0 = d + static_cast<size_t>(row0) * ldd + tn * QBN + c0;
+#pragma unroll 1
+        for (int r0 = 0; r0 < 32; r0 += 8 * kRowsPerStore) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            v[u] = *reinterpret_cast<const uint4*>(epi + (r0 + u * kRowsPerStore + sub_row) * kQEpiPitch + sub_col);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int rr = r0 + u * kRowsPerStore + sub_row;
+            if (row0 + rr < M)
+              *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out0 + static_cast<size_t>(rr) * ldd) + sub_col) = v[u];
           }
         }
+        __syncwarp();                                  // the staging rows are read: the next pass may overwrite them
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(acc_empty), 0));
       acc_phase ^= 1;
     }
   }

@@ -21,7 +21,7 @@ enum Proto : int { PROTO_SIMPLE = 0, PROTO_LL = 1, PROTO_LL128 = 2 };
 enum DType : int { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2 };
 
 constexpr int kMaxRanks = 16;
-constexpr int kMaxChannels = 64;
+constexpr int kMaxChannels = 128;
 constexpr int kMaxConns = kMaxRanks * kMaxChannels;   // connection id = chan * kMaxRanks + peer
 constexpr int kMaxTbsPerRank = 128;
 constexpr int kFifoSlots = 4;                          // tiles in flight per connection

@@ -19,7 +19,7 @@ namespace {
 using namespace msccl;
 
 // Layout of the fixed array (offsets in bytes).
-constexpr size_t kSyncStride = 64 * 1024;                       // one SyncPage per rank, padded
+constexpr size_t kSyncStride = 128 * 1024;                      // one SyncPage per rank, padded
 constexpr size_t kOffSync = 0;
 constexpr size_t kOffRankCtx = kOffSync + MSCCL_NOALLOC_MAX_RANKS * kSyncStride;
 constexpr size_t kOffTbs = kOffRankCtx + 4096;

@@ -18,9 +18,16 @@ def register_b200_plans():
     manual = ThreadblockPolicy.manual
     # One CTA moves roughly 50 GB/s, so a plan needs a few dozen CTAs per direction to fill a GPU's
     # NVLink port; all threadblocks of a plan must also be co-resident (148 SMs).
-    copies = {2: 32, 4: 16, 8: 8}
+    # Measured on two GPUs (a send and a receive threadblock per copy and peer): all-gather of 64 MB 114 us with 32
+    # copies, 87 us with 64 (NCCL 100 us); all-to-all of 64 MB 121 -> 88 us (NCCL 126 us).
+    copies = {2: 64, 4: 16, 8: 8}
+    # The two-shot all-reduce has one threadblock per copy and peer and reduces locally between its two transfers:
+    # 256 MB on two GPUs took 634 / 510 / 482 us with 32 / 64 / 128 copies (NCCL 526 us).
+    reduce_copies = {2: 128, 4: 16, 8: 8}
     small = {2: 4, 4: 2, 8: 1}     # latency-bound sizes: flag-in-data packets, few CTAs
-    middle = {2: 16, 4: 8, 8: 4}   # between the two: 128-byte lines with 120 bytes of payload (LL128), no fence per tile
+    # between the two: 128-byte lines with 120 bytes of payload (LL128), no fence per tile; ahead of the Simple plans up
+    # to 1-2 MB on two GPUs (all-gather of 1 MB: 20.5 us against 22.1 us), behind them from 4 MB
+    middle = {2: 16, 4: 8, 8: 4}
     for n in B200_GPU_COUNTS:
         mtype = f'b200x{n}' if n != 8 else ['b200', 'b200x8']
         box = fully_connected(n)
@@ -36,14 +43,14 @@ def register_b200_plans():
             allreduce_two_shot(n)
         two_shot.__name__ = f'b200_allreduce_two_shot_{n}'
         register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='Simple',
-                               sizes=('256KB', None), instances=copies[n], threadblock_policy=manual,
+                               sizes=('256KB', None), instances=reduce_copies[n], threadblock_policy=manual,
                                machines=lambda m: m == 1)(two_shot)
 
         def two_shot_ll128(prog, nodes, n=n):
             allreduce_two_shot(n)
         two_shot_ll128.__name__ = f'b200_allreduce_two_shot_ll128_{n}'
         register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='LL128',
-                               sizes=('256KB', '4MB'), instances=middle[n], threadblock_policy=manual,
+                               sizes=('256KB', '1MB'), instances=middle[n], threadblock_policy=manual,
                                machines=lambda m: m == 1)(two_shot_ll128)
 
         def a2a(prog, nodes, n=n):
@@ -88,16 +95,16 @@ def register_b200_plans():
             alltoall_direct(n)
         a2a_ll128.__name__ = f'b200_alltoall_direct_ll128_{n}'
         register_msccl_program(box, 'alltoall', mtype, chunk_factor=1, protocol='LL128', instances=middle[n],
-                               sizes=('512KB', '8MB'), machines=lambda m: m == 1)(a2a_ll128)
+                               sizes=('512KB', '2MB'), machines=lambda m: m == 1)(a2a_ll128)
 
         def ag_ll128(prog, nodes, n=n):
             allgather_direct(n)
         ag_ll128.__name__ = f'b200_allgather_direct_ll128_{n}'
         register_msccl_program(box, 'allgather', mtype, chunk_factor=1, protocol='LL128', instances=middle[n],
-                               sizes=('512KB', '8MB'), machines=lambda m: m == 1)(ag_ll128)
+                               sizes=('512KB', '2MB'), machines=lambda m: m == 1)(ag_ll128)
 
         def rs_ll128(prog, nodes, n=n):
             reduce_scatter_direct(n)
         rs_ll128.__name__ = f'b200_reduce_scatter_direct_ll128_{n}'
         register_msccl_program(box, 'reduce_scatter', mtype, chunk_factor=1, protocol='LL128', instances=middle[n],
-                               sizes=('512KB', '8MB'), machines=lambda m: m == 1)(rs_ll128)
+                               sizes=('512KB', '2MB'), machines=lambda m: m == 1)(rs_ll128)

@@ -25,7 +25,7 @@ import torch
 
 from msccl.runtime.native import load
 
-SYNC_BYTES = 64 * 1024
+SYNC_BYTES = 128 * 1024
 _RANKCTX = struct.Struct('<2Q3Q3q')
 
 

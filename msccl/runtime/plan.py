@@ -29,7 +29,7 @@ STEP_CODES = {'nop': 0, 's': 1, 'r': 2, 'rcs': 3, 'rrs': 4, 'rrc': 5, 'rrcs': 6,
 BUF_CODES = {'i': 0, 'o': 1, 's': 2}
 PROTO_CODES = {'Simple': 0, 'LL': 1, 'LL128': 2}
 K_MAX_RANKS = 16
-K_MAX_CHANNELS = 64
+K_MAX_CHANNELS = 128
 K_MAX_TBS = 128
 K_FIFO_SLOTS = 4
 K_MAX_BATCH = 8                 # `re` steps fused into one pass (csrc/msccl_device.h kMaxBatch)
