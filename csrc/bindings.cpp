@@ -333,7 +333,7 @@ PYBIND11_MODULE(_msccl_native, m) {
   m.def("ag_gemm_mxfp8", [](uintptr_t x_local, uintptr_t sf_local, uintptr_t b, uintptr_t sfb, uintptr_t d, int rows_per_rank, int N,
                              int K, int ldb, int ldd, int rank, int nranks, int comm_ctas, uintptr_t heap_bases_dev,
                              std::vector<uintptr_t> heap_ptrs, size_t off_fused, uintptr_t mc_base, size_t gathered_off,
-                             size_t gathered_bytes, uintptr_t error_words, int epilogue, int grid, uintptr_t order, uintptr_t stream) {
+                             size_t gathered_bytes, uintptr_t error_words, int epilogue, int grid, uintptr_t order, uintptr_t stream, bool pair) {
     msccl::sm100::AgGemmF8Args g;
     std::memset(&g, 0, sizeof(g));
     g.x_local = reinterpret_cast<const void*>(x_local);
@@ -354,12 +354,13 @@ PYBIND11_MODULE(_msccl_native, m) {
     g.gathered_off = gathered_off;
     g.gathered_bytes = gathered_bytes;
     g.error_words = reinterpret_cast<int*>(error_words);
-    check_rt(msccl::sm100::launch_ag_gemm_mxfp8(g, epilogue, grid, as_stream(stream)), "launch of the fused fp8 all-gather GEMM kernel");
+    if (pair) check_rt(msccl::sm100::launch_ag_gemm_mxfp8_2cta(g, epilogue, grid, as_stream(stream)), "launch of the fused fp8 all-gather GEMM kernel (pairs)");
+    else check_rt(msccl::sm100::launch_ag_gemm_mxfp8(g, epilogue, grid, as_stream(stream)), "launch of the fused fp8 all-gather GEMM kernel");
   });
   m.def("gemm_rs_mxfp8", [](uintptr_t a, uintptr_t sfa, uintptr_t b, uintptr_t sfb, uintptr_t out, int rows_per_rank, int N, int K,
                              int lda, int ldb, int rank, int nranks, uintptr_t heap_bases_dev, std::vector<uintptr_t> heap_ptrs,
                              size_t off_fused, size_t partial_off, uintptr_t error_words, int grid, uintptr_t order,
-                             uintptr_t reduce_order, int reduce_ctas, uintptr_t stream) {
+                             uintptr_t reduce_order, int reduce_ctas, uintptr_t stream, bool pair) {
     msccl::sm100::GemmRsF8Args g;
     std::memset(&g, 0, sizeof(g));
     g.a = reinterpret_cast<const void*>(a);
@@ -377,7 +378,8 @@ PYBIND11_MODULE(_msccl_native, m) {
     g.order = reinterpret_cast<const int*>(order);
     g.reduce_order = reinterpret_cast<const int*>(reduce_order);
     g.reduce_ctas = reduce_ctas;
-    check_rt(msccl::sm100::launch_gemm_rs_mxfp8(g, grid, as_stream(stream)), "launch of the fused fp8 GEMM reduce-scatter kernel");
+    if (pair) check_rt(msccl::sm100::launch_gemm_rs_mxfp8_2cta(g, grid, as_stream(stream)), "launch of the fused fp8 GEMM reduce-scatter kernel (pairs)");
+    else check_rt(msccl::sm100::launch_gemm_rs_mxfp8(g, grid, as_stream(stream)), "launch of the fused fp8 GEMM reduce-scatter kernel");
   });
   m.def("sm_count", &msccl::sm100::sm_count);
   // bf16 [rows, K] -> e4m3 values and packed UE8M0 scale blocks (one pass)

@@ -99,6 +99,10 @@ struct GemmRsF8Args {
 };
 
 cudaError_t launch_ag_gemm(const AgGemmArgs& args, int epilogue, int grid, cudaStream_t stream);
+// the block-scaled fp8 kernels on CTA pairs (256 x 256 tiles; fused_tp_fp8_2cta.cu).  With the SwiGLU epilogue the
+// weight rows are interleaved per 256 (128 gate rows, 128 up rows) instead of per 128.
+cudaError_t launch_ag_gemm_mxfp8_2cta(const AgGemmF8Args& args, int epilogue, int grid, cudaStream_t stream);
+cudaError_t launch_gemm_rs_mxfp8_2cta(const GemmRsF8Args& args, int grid, cudaStream_t stream);
 // the same two kernels on CTA pairs (cta_group::2, 256 x 256 tiles; fused_tp_2cta.cu)
 cudaError_t launch_ag_gemm_2cta(const AgGemmArgs& args, int epilogue, int grid, cudaStream_t stream);
 cudaError_t launch_gemm_rs_2cta(const GemmRsArgs& args, int grid, cudaStream_t stream);

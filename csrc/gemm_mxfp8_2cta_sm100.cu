@@ -20,62 +20,13 @@
 
 #include "gemm_sm100.cuh"
 #include "gemm_sm100.h"
+#include "mxfp8_pair.cuh"
 #include "umma_2cta.cuh"
 
 namespace msccl {
 namespace sm100 {
 
 namespace {
-
-constexpr int QBM = 256, QBN = 256, QBK = 128;
-constexpr int kQStages = 5;                        // pipeline stages; the shared memory of a sixth holds the staged epilogue
-constexpr int kQGroupM = 8;
-constexpr int kQABytes = BM * QBK;                 // 16 KB: this CTA's 128 rows of A
-constexpr int kQBBytes = (QBN / 2) * QBK;          // 16 KB: this CTA's 128 rows of B
-constexpr int kQSfBytes = 512;                     // scales of 128 rows x 128 K
-constexpr int kQLoadBytes = kQABytes + kQBBytes + 3 * kQSfBytes;   // bytes one CTA loads per stage
-constexpr int kQStageBytes = 34 * 1024;            // stage pitch: operand tiles stay 1024-byte aligned
-constexpr int kQTmemCols = 512;                    // [0,256) accumulator, then 12 scale columns per stage
-constexpr int kQSfTmemBase = QBN;
-// Staged epilogue: an epilogue warp packs its 32 rows x kQStageCols columns to bf16 in shared memory (one row per
-// lane), then stores whole row segments with consecutive lanes on consecutive 16 bytes.  After the last pass into
-// shared memory the accumulator is free for the next tile while the stores are still being issued.
-constexpr int kQStageCols = 128;
-constexpr int kQEpiPitch = kQStageCols * 2 + 16;   // bytes per staged row (16 of padding spread the banks)
-constexpr int kQEpiPerWarp = 32 * kQEpiPitch;
-constexpr size_t kQSmemBytes = 1024 + static_cast<size_t>(kQStages) * kQStageBytes + 256 + 4 * kQEpiPerWarp;
-static_assert(kQLoadBytes <= kQStageBytes, "stage pitch too small");
-static_assert(kQSmemBytes <= 227 * 1024, "shared memory of one CTA");
-
-__device__ __forceinline__ void tma_load_2d_pair8(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ uint64_t smem_desc_scales_pair(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFF);
-  d |= static_cast<uint64_t>(128 >> 4) << 32;     // stride between the four 8-row groups of a 32 x 16-byte block
-  d |= static_cast<uint64_t>(1) << 46;
-  return d;
-}
-// Scales shared memory -> tensor memory in both CTAs of the pair (each from its own shared memory).
-__device__ __forceinline__ void tmem_cp_scales_pair(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-__device__ __forceinline__ uint32_t idesc_mxf8_pair(uint32_t sf) {
-  return (sf << 4) | (1u << 23) | (static_cast<uint32_t>(QBN >> 3) << 17) | (static_cast<uint32_t>(QBM >> 4) << 24) | (sf << 29);
-}
-__device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa_taddr,
-                                               uint32_t sfb_taddr, bool accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "r"(sfa_taddr), "r"(sfb_taddr)
-      : "memory");
-}
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_mxfp8_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,

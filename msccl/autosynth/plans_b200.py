@@ -7,7 +7,7 @@ which the executor provides natively (``msccl.language.ext_nvls``).
 from msccl.autosynth.registry import register_msccl_program
 from msccl.language.mscclir import ThreadblockPolicy
 from msccl.programs.allgather import allgather_direct, reduce_scatter_direct
-from msccl.programs.allreduce import allreduce_one_shot, allreduce_two_shot
+from msccl.programs.allreduce import allreduce_one_shot, allreduce_ring, allreduce_two_shot
 from msccl.programs.alltoall import alltoall_direct
 from msccl.topologies import fully_connected
 
@@ -42,9 +42,20 @@ def register_b200_plans():
         def two_shot(prog, nodes, n=n):
             allreduce_two_shot(n)
         two_shot.__name__ = f'b200_allreduce_two_shot_{n}'
-        register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='Simple',
-                               sizes=('256KB', None), instances=reduce_copies[n], threadblock_policy=manual,
-                               machines=lambda m: m == 1)(two_shot)
+        if n > 2:
+            register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='Simple',
+                                   sizes=('256KB', None), instances=reduce_copies[n], threadblock_policy=manual,
+                                   machines=lambda m: m == 1)(two_shot)
+        else:
+            # Two GPUs: the ring on two channels is the two-shot exchange with the receive, the reduction and the
+            # send back fused into one step (three steps per threadblock instead of five).  128 threadblocks:
+            # 39 / 61 / 157 / 492 us at 4 / 16 / 64 / 256 MB against 47 / 62 / 167 / 549 us for NCCL.
+            def ring(prog, nodes):
+                allreduce_ring(2, 2)
+            ring.__name__ = 'b200_allreduce_ring_2'
+            register_msccl_program(box, 'allreduce', mtype, chunk_factor=2, inplace=True, protocol='Simple',
+                                   sizes=('256KB', None), instances=reduce_copies[n] // 2, threadblock_policy=manual,
+                                   machines=lambda m: m == 1)(ring)
 
         def two_shot_ll128(prog, nodes, n=n):
             allreduce_two_shot(n)

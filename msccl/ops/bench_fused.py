@@ -86,7 +86,7 @@ def main(argv=None):
         out['gemm_rs'] = entry(timed(lambda: tp.gemm_reduce_scatter(h, wd, out=y)), flops_down, scattered_out * 2, args.peak_tflops)
     if 'ag_gemm_mxfp8' in only or 'gemm_rs_mxfp8' in only:
         pack = lambda s: pack_mx_scales(s, row_multiple=128)                                     # noqa: E731
-        guq, gus = quantize_mxfp8(interleave_gate_up(wg, wu, tile=128).float())
+        guq, gus = quantize_mxfp8(interleave_gate_up(wg, wu, tile=tp.mx_gate_up_tile).float())
         wdq, wds = quantize_mxfp8(wd.float())
         xq, xs = quantize_mxfp8(x.float())
         gus_p, wds_p, xs_p = pack(gus), pack(wds), pack(xs)

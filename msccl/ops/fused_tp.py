@@ -92,11 +92,18 @@ class FusedTensorParallel:
         return out
 
     # ---------------------------------------------------------------- block-scaled fp8 (OCP MX) operands
+    @property
+    def mx_gate_up_tile(self):
+        """Interleave width of gate and up rows the fp8 SwiGLU epilogue expects (``interleave_gate_up(..., tile=...)``):
+        256 on CTA pairs (128 gate + 128 up columns per tile), 128 on single CTAs."""
+        return 256 if self.pair else 128
+
     def all_gather_gemm_mxfp8(self, xq_local, sfx_packed, wq, sfw_packed, epilogue='none', out=None, stream=None):
         """The all-gather -> GEMM kernel on MX fp8 operands: ``xq_local`` [rows, hidden] e4m3 with its scales packed by
         ``msccl.ops.gemm.pack_mx_scales(scales, row_multiple=128)``, ``wq`` [N, hidden] e4m3 with packed scales.  What
         crosses NVLink is the fp8 block plus its scale blocks.  Returns bf16 ``[n*rows, N]`` (``N/2`` with ``swiglu``;
-        gate and up rows interleaved in groups of 64, ``interleave_gate_up(w_gate, w_up, tile=128)``)."""
+        gate and up rows interleaved with ``interleave_gate_up(w_gate, w_up, tile=self.mx_gate_up_tile)``).  Runs on
+        CTA pairs (256 x 256 tiles) when the row blocks pair up and N is a multiple of 256."""
         c = self.comm
         k = self.hidden
         assert xq_local.shape == (self.rows, k) and xq_local.is_contiguous() and xq_local.dtype == torch.float8_e4m3fn
@@ -112,11 +119,13 @@ class FusedTensorParallel:
         per_parity = -(-(self.n * self.rows * k + self.n * blocks * k_blocks * 512) // 1024) * 1024
         assert per_parity <= self.gathered_bytes
         stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        pair = self.pair and n_out % 256 == 0 and self.comm_ctas % 2 == 0
+        assert pair or not (swiglu and self.pair), 'with the SwiGLU epilogue on CTA pairs N must be a multiple of 256'
         c.native.ag_gemm_mxfp8(xq_local.data_ptr(), sfx_packed.data_ptr(), wq.data_ptr(), sfw_packed.data_ptr(), out.data_ptr(),
                                self.rows, n_out, k, wq.stride(0), out.stride(0), c.rank, self.n, self.comm_ctas,
                                c.dev_heap_bases, list(c.heap_ptrs), c.off_fused, c.mc_base, self.gathered_off, per_parity,
-                               _errors(xq_local.device).data_ptr(), 1 if swiglu else 0, self.grid or self.sms,
-                               self.ag_order.data_ptr(), stream_h)
+                               _errors(xq_local.device).data_ptr(), 1 if swiglu else 0, self.grid or (0 if pair else self.sms),
+                               self.ag_order.data_ptr(), stream_h, pair)
         self.launches += 1
         return out
 
@@ -134,10 +143,11 @@ class FusedTensorParallel:
             out = torch.empty(self.rows, self.hidden, dtype=torch.bfloat16, device=aq.device)
         assert out.is_contiguous()
         stream_h = (stream or torch.cuda.current_stream()).cuda_stream
+        pair = self.pair and self.hidden % 256 == 0
         c.native.gemm_rs_mxfp8(aq.data_ptr(), sfa_packed.data_ptr(), wq.data_ptr(), sfw_packed.data_ptr(), out.data_ptr(),
                                self.rows, self.hidden, k, aq.stride(0), wq.stride(0), c.rank, self.n, c.dev_heap_bases,
-                               list(c.heap_ptrs), c.off_fused, self.partial_off, _errors(aq.device).data_ptr(), self.sms,
-                               self.rs_order.data_ptr(), self.reduce_order.data_ptr(), min(self.reduce_ctas, self.sms - 1),
-                               stream_h)
+                               list(c.heap_ptrs), c.off_fused, self.partial_off, _errors(aq.device).data_ptr(),
+                               0 if pair else self.sms, self.rs_order.data_ptr(), self.reduce_order.data_ptr(),
+                               min(self.reduce_ctas, self.sms - 1), stream_h, pair)
         self.launches += 1
         return out

@@ -32,7 +32,7 @@ class TensorParallelMLP:
         self.fused = FusedTensorParallel(comm, tokens_per_rank, hidden)
         self.h = torch.empty(comm.world * tokens_per_rank, self.shard, dtype=torch.bfloat16, device=dev)
         if precision == 'mxfp8':
-            gu = interleave_gate_up(w_gate, w_up, tile=128)          # the fp8 kernel's tiles are 128 columns wide
+            gu = interleave_gate_up(w_gate, w_up, tile=self.fused.mx_gate_up_tile)   # 256 on CTA pairs, 128 on single CTAs
             self.wq_gate_up, s = quantize_mxfp8(gu.float())
             self.sf_gate_up = pack_mx_scales(s, row_multiple=128)
             self.wq_down, s = quantize_mxfp8(self.w_down.float())

@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 CSRC = os.path.join(ROOT, 'csrc')
 MODULE = '_msccl_native'
 ARCH_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a']
-SOURCES = ['exec_kernel.cu', 'direct_kernels.cu', 'gemm_sm100.cu', 'gemm_2cta_sm100.cu', 'gemm_mxfp8_sm100.cu', 'gemm_mxfp8_2cta_sm100.cu', 'fused_tp.cu', 'fused_tp_2cta.cu', 'fused_tp_fp8.cu', 'quantize_mx.cu', 'moe_a2a.cu', 'moe_a2a_2cta.cu', 'moe_route.cu', 'no_alloc.cu',
+SOURCES = ['exec_kernel.cu', 'direct_kernels.cu', 'gemm_sm100.cu', 'gemm_2cta_sm100.cu', 'gemm_mxfp8_sm100.cu', 'gemm_mxfp8_2cta_sm100.cu', 'fused_tp.cu', 'fused_tp_2cta.cu', 'fused_tp_fp8.cu', 'fused_tp_fp8_2cta.cu', 'quantize_mx.cu', 'moe_a2a.cu', 'moe_a2a_2cta.cu', 'moe_route.cu', 'no_alloc.cu',
            'symm_mem.cpp', 'bindings.cpp']
 
 

@@ -67,7 +67,11 @@ def check(comm, rank, n, rows, hidden, ffn_shard, calls=3):
         err = (y.float() - want_y).abs().max().item()
         assert err <= 3e-2 * want_y.abs().max().item() + 1e-3, ('gemm_rs', call, err)
     dist.barrier()
+    assert tp.pair and tp.mx_gate_up_tile == 256, 'CTA pairs are the default when the row blocks pair up'
     check_mxfp8(tp, comm, rank, n, rows, hidden, ffn_shard, gen)
+    tp.pair = False                                         # the single-CTA block-scaled kernels
+    check_mxfp8(tp, comm, rank, n, rows, hidden, ffn_shard, gen)
+    tp.pair = True
 
 
 def check_mxfp8(tp, comm, rank, n, rows, hidden, ffn_shard, gen):
@@ -79,9 +83,11 @@ def check_mxfp8(tp, comm, rank, n, rows, hidden, ffn_shard, gen):
     wgq, wgs = quantize_mxfp8(wg)
     wuq, wus = quantize_mxfp8(wu)
     wdq, wds = quantize_mxfp8(wd)
-    # gate and up rows interleaved in groups of 64: the scales are per row, so they interleave the same way
-    guq = interleave_gate_up(wgq.view(torch.uint8), wuq.view(torch.uint8), tile=128).view(torch.float8_e4m3fn)
-    gus = interleave_gate_up(wgs, wus, tile=128)
+    # gate and up rows interleaved in groups of 64 (single CTAs) or 128 (CTA pairs): the scales are per row, so they
+    # interleave the same way
+    tile = tp.mx_gate_up_tile
+    guq = interleave_gate_up(wgq.view(torch.uint8), wuq.view(torch.uint8), tile=tile).view(torch.float8_e4m3fn)
+    gus = interleave_gate_up(wgs, wus, tile=tile)
     pack = lambda t: pack_mx_scales(t, row_multiple=128)                                  # noqa: E731
     for call in range(3):
         x = torch.randn(rows, hidden, device='cuda', generator=gen)
