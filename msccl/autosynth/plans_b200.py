@@ -4,11 +4,12 @@ Size ranges follow the latency/bandwidth trade-off of the algorithms: one-shot w
 dominates, two-shot in the middle, and for large messages the in-switch (NVLS) reduction,
 which the executor provides natively (``msccl.language.ext_nvls``).
 """
-from msccl.autosynth.registry import register_msccl_program
+from msccl.autosynth.registry import register_msccl_program, register_synthesis_plan
 from msccl.language.mscclir import ThreadblockPolicy
 from msccl.programs.allgather import allgather_direct, reduce_scatter_direct
 from msccl.programs.allreduce import allreduce_one_shot, allreduce_ring, allreduce_two_shot
 from msccl.programs.alltoall import alltoall_direct
+from msccl.language.ext_nvls import allreduce_nvls
 from msccl.topologies import fully_connected
 
 B200_GPU_COUNTS = (2, 4, 8)
@@ -22,8 +23,10 @@ def register_b200_plans():
     # copies, 87 us with 64 (NCCL 100 us); all-to-all of 64 MB 121 -> 88 us (NCCL 126 us).
     copies = {2: 64, 4: 16, 8: 8}
     # The two-shot all-reduce has one threadblock per copy and peer and reduces locally between its two transfers:
-    # 256 MB on two GPUs took 634 / 510 / 482 us with 32 / 64 / 128 copies (NCCL 526 us).
-    reduce_copies = {2: 128, 4: 16, 8: 8}
+    # 256 MB on two GPUs took 634 / 510 / 482 us with 32 / 64 / 128 copies (NCCL 526 us), on four GPUs 1132 / 918 us with
+    # 16 / 32 copies (NCCL 682 us, which reduces inside the switch; so does the in-switch program of
+    # msccl.language.ext_nvls on registered tensors: 604 us).
+    reduce_copies = {2: 128, 4: 32, 8: 8}
     small = {2: 4, 4: 2, 8: 1}     # latency-bound sizes: flag-in-data packets, few CTAs
     # between the two: 128-byte lines with 120 bytes of payload (LL128), no fence per tile; ahead of the Simple plans up
     # to 1-2 MB on two GPUs (all-gather of 1 MB: 20.5 us against 22.1 us), behind them from 4 MB
@@ -36,33 +39,47 @@ def register_b200_plans():
             allreduce_one_shot(n)
         one_shot.__name__ = f'b200_allreduce_one_shot_{n}'
         register_msccl_program(box, 'allreduce', mtype, chunk_factor=1, inplace=True, protocol='LL',
-                               sizes=(0, '256KB'), threadblock_policy=manual,
+                               sizes=(0, '256KB' if n > 2 else '32KB'), threadblock_policy=manual,
                                machines=lambda m: m == 1)(one_shot)
 
         def two_shot(prog, nodes, n=n):
             allreduce_two_shot(n)
         two_shot.__name__ = f'b200_allreduce_two_shot_{n}'
-        if n > 2:
-            register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='Simple',
-                                   sizes=('256KB', None), instances=reduce_copies[n], threadblock_policy=manual,
-                                   machines=lambda m: m == 1)(two_shot)
-        else:
-            # Two GPUs: the ring on two channels is the two-shot exchange with the receive, the reduction and the
-            # send back fused into one step (three steps per threadblock instead of five).  128 threadblocks:
-            # 39 / 61 / 157 / 492 us at 4 / 16 / 64 / 256 MB against 47 / 62 / 167 / 549 us for NCCL.
-            def ring(prog, nodes):
-                allreduce_ring(2, 2)
-            ring.__name__ = 'b200_allreduce_ring_2'
-            register_msccl_program(box, 'allreduce', mtype, chunk_factor=2, inplace=True, protocol='Simple',
-                                   sizes=('256KB', None), instances=reduce_copies[n] // 2, threadblock_policy=manual,
-                                   machines=lambda m: m == 1)(ring)
 
         def two_shot_ll128(prog, nodes, n=n):
             allreduce_two_shot(n)
         two_shot_ll128.__name__ = f'b200_allreduce_two_shot_ll128_{n}'
-        register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='LL128',
-                               sizes=('256KB', '1MB'), instances=middle[n], threadblock_policy=manual,
-                               machines=lambda m: m == 1)(two_shot_ll128)
+        if n > 2:
+            register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='Simple',
+                                   sizes=('256KB', None), instances=reduce_copies[n], threadblock_policy=manual,
+                                   machines=lambda m: m == 1)(two_shot)
+            register_msccl_program(box, 'allreduce', mtype, chunk_factor=n, inplace=True, protocol='LL128',
+                                   sizes=('256KB', '1MB'), instances=middle[n], threadblock_policy=manual,
+                                   machines=lambda m: m == 1)(two_shot_ll128)
+            # From 4 GPUs up the reduction belongs into the switch: the program of in-switch steps (one multimem
+            # load-reduce and one multimem store per vector; `msccl.language.ext_nvls`) is what NCCL's NVLS algorithm
+            # does too, and no program of peer stores can match it (four GPUs, 64 MB: two-shot over peer stores 275 us,
+            # NCCL 188 us, in-switch program 170 us on registered tensors).  Tensors that are not registered memory
+            # pass through registered staging slices.
+            def in_switch(machines, n=n):
+                return allreduce_nvls(n, 8, name=f'b200_allreduce_in_switch_{n}')
+            in_switch.__name__ = f'b200_allreduce_in_switch_{n}'
+            register_synthesis_plan('allreduce', mtype, machines=lambda m: m == 1, sizes=('4MB', None))(in_switch)
+        else:
+            # Two GPUs: the ring on two channels is the two-shot exchange with the receive, the reduction and the
+            # send back fused into one step (three steps per threadblock instead of five).  Measured against NCCL
+            # on the same box:
+            #   LL, 32 threadblocks      19.0 / 18.5 / 20.6 us at 64 KB / 256 KB / 1 MB    (NCCL 22.0 / 20.1 / 20.1)
+            #   LL128, 32 threadblocks   36.5 us at 4 MB                                    (NCCL 40.2; Simple 39.2)
+            #   Simple, 128 threadblocks 61 / 157 / 492 us at 16 / 64 / 256 MB              (NCCL 62 / 167 / 549)
+            for proto, low, high, inst in (('LL', '32KB', '2MB', 16), ('LL128', '2MB', '8MB', 16),
+                                           ('Simple', '8MB', None, reduce_copies[2] // 2)):
+                def ring(prog, nodes):
+                    allreduce_ring(2, 2)
+                ring.__name__ = 'b200_allreduce_ring_2' + {'LL': '_ll', 'LL128': '_ll128', 'Simple': ''}[proto]
+                register_msccl_program(box, 'allreduce', mtype, chunk_factor=2, inplace=True, protocol=proto,
+                                       sizes=(low, high), instances=inst, threadblock_policy=manual,
+                                       machines=lambda m: m == 1)(ring)
 
         def a2a(prog, nodes, n=n):
             alltoall_direct(n)

@@ -87,6 +87,8 @@ class Executor:
         # how the warps of a CTA learn that a step may start: 'poll' shared memory, or at a CTA 'barrier'
         self.wait_mode = 0 if os.environ.get('MSCCL_EXEC_WAIT', 'barrier') == 'poll' else 1
         self._scratch_pool = None  # registered scratch shared by all plans (one process per GPU)
+        self._stage = None         # registered staging slices for in-switch programs on ordinary tensors
+        self.launches_staged = 0
 
     # ------------------------------------------------------------------ plans
     def compile(self, algo_or_xml) -> DevicePlan:
@@ -285,9 +287,12 @@ class Executor:
         t_in = inputs[rank]
         offset = comm.heap_offset_of(t_in)
         nbytes = t_in.numel() * t_in.element_size()
-        if offset is None or not t_in.is_contiguous() or nbytes % (16 * world) or t_in.dtype not in DTYPE_CODES:
-            raise PlanError('in-switch programs need a contiguous tensor from Communicator.symmetric_empty whose size is '
-                            'a multiple of 16 bytes per rank')
+        if not t_in.is_contiguous() or nbytes % (16 * world) or t_in.dtype not in DTYPE_CODES:
+            raise PlanError('in-switch programs need a contiguous tensor whose size is a multiple of 16 bytes per rank')
+        if offset is None:
+            if plan.nvls_kind != 'allreduce':
+                raise PlanError('in-switch all-gather / reduce-scatter programs need tensors from Communicator.symmetric_empty')
+            return {rank: self._staged_in_switch_allreduce(t_in, stream)}
         stream_h = (stream or torch.cuda.current_stream()).cuda_stream
         code = DTYPE_CODES[t_in.dtype]
         nat = comm.native
@@ -312,6 +317,71 @@ class Executor:
         self.launches += 1
         self.last_algorithm = f'in-switch {plan.nvls_kind}'
         return {rank: result}
+
+    STAGE_SLICE_BYTES = 64 << 20
+
+    def _staged_in_switch_allreduce(self, tensor, stream):
+        """The in-switch all-reduce on a tensor that is not registered memory: the tensor passes through two registered
+        slices of 64 MB.  A tensor that fits into one slice is copied in, reduced and copied back on the caller's stream.
+        Larger ones are cut into slices whose copies run on two side streams, so the copy-in of slice i + 1 and the
+        copy-out of slice i - 1 overlap the in-switch kernel of slice i (which keeps 8 SMs busy); a slice is reused only
+        after its copy-out, and the kernel's closing barrier means no peer still reads it."""
+        comm = self.comm
+        world, rank = comm.world, comm.rank
+        esize = tensor.element_size()
+        nbytes = tensor.numel() * esize
+        slice_bytes = self.STAGE_SLICE_BYTES // (16 * world) * (16 * world)
+        if self._stage is None:
+            buf = comm.symmetric_empty(2 * slice_bytes, torch.uint8)[0]
+            self._stage = (buf, comm.heap_offset_of(buf), torch.cuda.Stream(), torch.cuda.Stream(),
+                           [torch.cuda.Event(), torch.cuda.Event()])
+        buf, base, s_in, s_out, freed = self._stage
+        main = stream or torch.cuda.current_stream()
+        flat = tensor.view(-1).view(torch.uint8)
+        code = DTYPE_CODES[tensor.dtype]
+        pipelined = os.environ.get('MSCCL_TWOSHOT_PIPE', '0') == '1'
+        if nbytes <= slice_bytes:
+            if self.launches_staged:
+                main.wait_event(freed[0])                       # an earlier, sliced call may still copy out of slice 0
+            stage = buf[:nbytes]
+            with torch.cuda.stream(main):
+                stage.copy_(flat, non_blocking=True)
+                comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, base, nbytes, code, rank, world, comm.dev_syncs,
+                                              comm.timeout_ns, 8, main.cuda_stream, pipelined=pipelined)
+                flat.copy_(stage, non_blocking=True)
+                freed[0].record(main)
+            self.launches += 1
+            self.launches_staged += 1
+            self.last_algorithm = 'in-switch allreduce (staged)'
+            return tensor
+        start = torch.cuda.Event()
+        start.record(main)
+        s_in.wait_event(start)                                  # the tensor's producer
+        pieces = [(o, min(slice_bytes, nbytes - o)) for o in range(0, nbytes, slice_bytes)]
+        for i, (off, size) in enumerate(pieces):
+            half = i & 1
+            stage = buf[half * slice_bytes: half * slice_bytes + size]
+            if i >= 2 or self.launches_staged:
+                s_in.wait_event(freed[half])                    # the copy-out that last used this slice
+            with torch.cuda.stream(s_in):
+                stage.copy_(flat[off:off + size], non_blocking=True)
+                loaded = torch.cuda.Event()
+                loaded.record(s_in)
+            main.wait_event(loaded)
+            comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, base + half * slice_bytes, size, code, rank, world,
+                                          comm.dev_syncs, comm.timeout_ns, 8, main.cuda_stream, pipelined=pipelined)
+            reduced = torch.cuda.Event()
+            reduced.record(main)
+            s_out.wait_event(reduced)
+            with torch.cuda.stream(s_out):
+                flat[off:off + size].copy_(stage, non_blocking=True)
+                freed[half].record(s_out)
+            self.launches += 1
+        for ev in freed[:min(2, len(pieces))]:
+            main.wait_event(ev)
+        self.launches_staged += 1
+        self.last_algorithm = 'in-switch allreduce (staged)'
+        return tensor
 
     # -------------------------------------------------------------- collectives
     def all_reduce(self, tensor, stream=None, algorithm='auto'):

@@ -44,7 +44,7 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group('nccl', device_id=torch.device('cuda', local))
     rank, n = dist.get_rank(), dist.get_world_size()
-    comm = Communicator.from_process_group(fifo_bytes=64 << 20, arena_bytes=96 << 20)
+    comm = Communicator.from_process_group(fifo_bytes=64 << 20, arena_bytes=320 << 20)
     ex = Executor(comm)
     if rank == 0:
         print(f'communicator: mode={comm.mode} multicast={"yes" if comm.mc_base else "no"} world={n}', flush=True)
@@ -165,8 +165,22 @@ def main():
         ex.check()
         assert torch.equal(view.cpu(), torch.cat([p[:8192] for p in parts]))
         dist.barrier()
+        # the in-switch all-reduce on a tensor that is not registered memory: staged through registered slices,
+        # here two and a half of them, twice in a row (the slices are reused)
+        big = (ex.STAGE_SLICE_BYTES * 5 // 2) // (2 * 16 * n) * (16 * n)     # elements of bf16
+        gen = torch.Generator(device='cuda').manual_seed(1000 + rank)
+        plan_sw = ex.compile(allreduce_nvls(n, 8))
+        for numel in (n * 8192, big, n * 65536, big):        # one slice on the caller's stream / slices on side streams
+            plain = torch.randn(numel, device='cuda', generator=gen).bfloat16()
+            want = plain.clone()
+            dist.all_reduce(want)
+            got = ex.run(plan_sw, plain)[rank]
+            ex.check()
+            assert ex.last_algorithm == 'in-switch allreduce (staged)' and got.data_ptr() == plain.data_ptr()
+            assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2 * n), ('staged in-switch all-reduce', numel)
+        dist.barrier()
         if rank == 0:
-            print('in-switch programs: executed by the multimem kernels', flush=True)
+            print('in-switch programs: executed by the multimem kernels, ordinary tensors staged', flush=True)
 
     # 3b. direct all-gather / all-to-all / reduce-scatter on symmetric memory (sizes with a ragged tail per CTA)
     for blk in (2048, 1 << 16, (1 << 18) + 4096):

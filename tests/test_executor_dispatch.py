@@ -127,9 +127,10 @@ def test_in_switch_programs_go_to_the_native_kernels(ex):
     out = ex.run(plan, t, stream=s)[rank]
     assert out.numel() == 4096 and last(ex)[0] == 'twoshot_allreduce' and last(ex)[1][-1] == out.data_ptr()
     assert ex.last_algorithm == 'in-switch reduce_scatter'
-    # needs registered memory and a multicast window
+    # gather-type in-switch programs need registered memory (the all-reduce stages ordinary tensors through registered
+    # slices, which needs a GPU); every in-switch program needs a multicast window
     with pytest.raises(PlanError):
-        ex.run(ex.compile(allreduce_nvls(n)), torch.zeros(n * 4096, dtype=torch.bfloat16), stream=s)
+        ex.run(ex.compile(allgather_nvls(n)), torch.zeros(n * 4096, dtype=torch.bfloat16), stream=s)
     plain = Executor(FakeComm(multicast=False))
     with pytest.raises(PlanError):
         plain.run(plain.compile(allreduce_nvls(n)), plain.comm.symmetric(n * 4096, torch.bfloat16), stream=s)

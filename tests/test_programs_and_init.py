@@ -129,7 +129,8 @@ def test_init_b200_plan_table(capsys, clean_env):
     assert 'b200_allreduce_two_shot_ll128_8 with LL128 protocol' in out          # 128-byte lines between the two
     assert 'b200_alltoall_direct_ll128_8 with LL128 protocol' in out
     root = ET.parse(os.environ['MSCCL_CONFIG']).getroot()
-    assert root.tag == 'msccl_algos' and len(root.findall('load')) == 5
+    assert 'b200_allreduce_in_switch_8' in out                                     # large messages: reduced inside the switch
+    assert root.tag == 'msccl_algos' and len(root.findall('load')) == 6
     assert [e.get('proto') for e in root.findall('load')].count('LL128') == 2
     for entry in load_plan_table(os.environ['MSCCL_CONFIG']):
         assert validate(entry.algo) == [] and entry.algo.ngpus == 8
@@ -166,3 +167,28 @@ def test_plan_listing_matches_reference_rows():
                  ['ndv4', 'alltoall', '2,4', '1 KB', 'infinity', 'Simple', '0', 'run ndv4_alltoall_hierarchical_config2'],
                  ['ndv4', 'alltoall', '64', '32 MB', 'infinity', 'Simple', '0', 'run ndv4_alltoall_three_step']]:
         assert want in rows, want
+
+
+@pytest.mark.parametrize('machine', ['b200x2', 'b200x4', 'b200x8'])
+def test_every_registered_b200_plan_fits_the_executor(machine):
+    # each registered plan compiles to tables within the executor's limits (threadblocks per rank, channels, steps)
+    from msccl.autosynth.registry import synthesis_plans
+    from msccl.language.ext_nvls import classify
+    from msccl.runtime.plan import K_MAX_CHANNELS, K_MAX_TBS, compile_plan
+    from msccl.xml import load_xml_file
+    import msccl.autosynth.plans_b200  # noqa: F401  (registers on import)
+    seen = 0
+    for (coll, mtype), entries in list(synthesis_plans.items()):
+        if mtype != machine:
+            continue
+        for entry in entries:
+            algo = load_xml_file(entry[1](1))
+            assert validate(algo) == [], algo.name
+            if classify(algo) is not None:           # a program of in-switch steps runs on the native kernel of its shape
+                seen += 1
+                continue
+            plan = compile_plan(algo, [0], 64 << 10)
+            assert algo.nchannels <= K_MAX_CHANNELS and len(algo.gpus[0].tbs) <= K_MAX_TBS, algo.name
+            assert plan.total_tbs() == len(algo.gpus[0].tbs)
+            seen += 1
+    assert seen >= 10
