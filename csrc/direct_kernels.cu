@@ -51,7 +51,7 @@ __device__ bool rank_barrier(SyncPage* const* syncs, int rank, int nranks, unsig
   __syncthreads();
   if (threadIdx.x < nranks) {
     const unsigned long long e = me->cta_epoch[lane] + 1;
-    __threadfence_system();
+    fence_acq_rel_sys();
     st_release_sys(&syncs[threadIdx.x]->cta_barrier[lane][rank], e);
     unsigned int spins = 0;
     while (ld_acquire_sys(&me->cta_barrier[lane][threadIdx.x]) < e) {

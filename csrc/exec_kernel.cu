@@ -652,7 +652,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
 
       // ---- signals (one thread; the other warps go on to the next step's waits) ----
       if (tid == 0) {
-        // One fence covers everything this step publishes (a system-scope fence costs microseconds, so the flags
+        // One fence covers everything this step publishes (a system-scope fence costs a microsecond or more, so the flags
         // themselves are relaxed stores behind it): the tile written by all warps before the barrier comes before
         // its count; this rank's own accesses to a slot come before the slot is opened; the step's stores come
         // before the progress word other threadblocks wait on.  The credit alone needs no fence: every warp has used
@@ -665,7 +665,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_kernel(ExecArgs a) {
           any_dep = any_dep || sp[s + k].hasdep != 0;
         }
         const bool publishes_tile = sends && PROTO == PROTO_SIMPLE;
-        if (publishes_tile || more > 0) __threadfence_system();
+        if (publishes_tile || more > 0) fence_acq_rel_sys();
         else if (any_dep) __threadfence();
         if (publishes_tile) {
           const unsigned int bit = 1u << static_cast<int>(sseq % kFifoSlots);

@@ -53,10 +53,10 @@ __device__ __forceinline__ void push_f8_blocks(const AgGemmF8Args& g, FusedPage*
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-      __threadfence_system();
+      fence_acq_rel_sys();
       if (atomicAdd(&page->ag_block_count[b], 1u) == static_cast<unsigned int>(parts) - 1u) {
         page->ag_block_count[b] = 0;
-        __threadfence_system();
+        fence_acq_rel_sys();
         for (int q = 1; q < g.nranks; ++q)
           st_release_sys(&g.pages[(g.rank + q) % g.nranks]->ag_flag[g.rank][b], epoch);
       }

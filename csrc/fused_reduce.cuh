@@ -11,31 +11,40 @@ namespace sm100 {
 constexpr int kReduceSlices = 8;       // a row block is reduced in this many independent pieces
 
 // Sum of the n partial slabs over 16-byte vectors [first, first + count) of this rank's shard, in rank order, fp32
-// accumulation, one rounding to bf16.  RU vectors per thread and pass: RU x n loads in flight per thread.
-template <int RU, typename Args>
+// accumulation, one rounding to bf16.  RU vectors per thread and pass; the loads of NR sources are all issued before
+// the first add (the loop over sources is unrolled for that), so RU x NR loads are in flight per thread.  The number
+// of ranks is a multiple of NR (NR = 1 serves any count).
+template <int RU, int NR, typename Args>
 __device__ __forceinline__ void reduce_vectors(const Args& g, const char* my_slabs, size_t slab_bytes, size_t first, size_t count) {
   char* out = static_cast<char*>(g.out);
   const size_t stride = blockDim.x;
+#pragma unroll 1
   for (size_t i = threadIdx.x; i < count; i += stride * RU) {
     float acc[RU][8];
 #pragma unroll
     for (int u = 0; u < RU; ++u)
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[u][e] = 0.0f;
-    for (int s = 0; s < g.nranks; ++s) {
-      uint4 in[RU];
+#pragma unroll 1
+    for (int s0 = 0; s0 < g.nranks; s0 += NR) {
+      uint4 in[NR][RU];
 #pragma unroll
-      for (int u = 0; u < RU; ++u) {
-        const size_t ii = i + u * stride;
-        if (ii < count) in[u] = *reinterpret_cast<const uint4*>(my_slabs + s * slab_bytes + (first + ii) * 16);
-      }
+      for (int r = 0; r < NR; ++r)
 #pragma unroll
-      for (int u = 0; u < RU; ++u) {
-        const uint32_t w[4] = {in[u].x, in[u].y, in[u].z, in[u].w};
+        for (int u = 0; u < RU; ++u) {
+          const size_t ii = i + u * stride;
+          if (ii < count) in[r][u] = *reinterpret_cast<const uint4*>(my_slabs + (s0 + r) * slab_bytes + (first + ii) * 16);
+        }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          acc[u][2 * e] += __uint_as_float(w[e] << 16);
-          acc[u][2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+      for (int r = 0; r < NR; ++r) {
+#pragma unroll
+        for (int u = 0; u < RU; ++u) {
+          const uint32_t w[4] = {in[r][u].x, in[r][u].y, in[r][u].z, in[r][u].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[u][2 * e] += __uint_as_float(w[e] << 16);
+            acc[u][2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+          }
         }
       }
     }
@@ -89,9 +98,10 @@ __device__ __forceinline__ void reduce_items(const Args& g, FusedPage* page, con
     const size_t count = min(block_vectors, begin + slice_vectors) - begin;
     const size_t first = static_cast<size_t>(b) * block_vectors + begin;
     // keep about 16 loads per thread in flight whatever the number of ranks
-    if (g.nranks <= 2) reduce_vectors<8>(g, my_slabs, slab_bytes, first, count);
-    else if (g.nranks <= 4) reduce_vectors<4>(g, my_slabs, slab_bytes, first, count);
-    else reduce_vectors<2>(g, my_slabs, slab_bytes, first, count);
+    if (g.nranks == 2) reduce_vectors<4, 2>(g, my_slabs, slab_bytes, first, count);
+    else if (g.nranks == 4) reduce_vectors<4, 4>(g, my_slabs, slab_bytes, first, count);
+    else if (g.nranks % 8 == 0) reduce_vectors<2, 8>(g, my_slabs, slab_bytes, first, count);
+    else reduce_vectors<4, 1>(g, my_slabs, slab_bytes, first, count);
   }
 }
 

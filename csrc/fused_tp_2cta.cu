@@ -92,10 +92,10 @@ ag_gemm_2cta_kernel(const __grid_constant__ CUtensorMap map_local, const __grid_
       }
       __syncthreads();
       if (threadIdx.x == 0) {
-        __threadfence_system();
+        fence_acq_rel_sys();
         if (atomicAdd(&page->ag_block_count[b], 1u) == static_cast<unsigned int>(parts) - 1u) {
           page->ag_block_count[b] = 0;
-          __threadfence_system();
+          fence_acq_rel_sys();
           for (int q = 1; q < g.nranks; ++q)
             st_release_sys(&g.pages[(g.rank + q) % g.nranks]->ag_flag[g.rank][b], epoch);
         }
@@ -317,6 +317,7 @@ gemm_rs_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int quarter = warp % 4;
       int acc = 0;
       uint32_t acc_phase = 0;
+      int pend_owner = -1, pend_b = 0;                      // the tile whose stores were issued last
       for (int tile = cluster; tile < num_tiles; tile += pairs) {
         const int tn = tile % tiles_n, rb = 2 * (tile / tiles_n) + static_cast<int>(cta_rank);
         const int owner = g.order[2 * rb], b = g.order[2 * rb + 1];
@@ -335,6 +336,9 @@ gemm_rs_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&p.acc_empty[acc]), 0));   // free as soon as it sits in shared memory
+        // count the previous tile on its owner: its stores were issued a whole tile ago, so the release has nothing
+        // left to wait for (a release right behind the stores, let alone a system-scope fence, cost 8-30 us a tile)
+        if (pend_owner >= 0 && lane == 0) red_add_release_sys(&g.pages[pend_owner]->rs_count[g.rank][pend_b], 1ull);
         // one row (512 contiguous bytes) per store instruction, 8 rows in flight
         char* dst0 = slab + ((static_cast<size_t>(b) * BM + quarter * 32) * g.N + static_cast<size_t>(tn) * PBN) * 2 + lane * 16;
 #pragma unroll 1
@@ -346,13 +350,12 @@ gemm_rs_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int u = 0; u < 8; ++u) *reinterpret_cast<uint4*>(dst0 + static_cast<size_t>(r0 + u) * g.N * 2) = d[u];
         }
         __syncwarp();
-        // this quarter of the tile is on its way: make it visible on the owner, then count it there
-        if (lane == 0) {
-          __threadfence_system();
-          red_add_release_sys(&g.pages[owner]->rs_count[g.rank][b], 1ull);
-        }
+        pend_owner = owner;                                  // published while the next tile is staged (or after the loop)
+        pend_b = b;
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
+      // the last tile of this warp
+      if (pend_owner >= 0 && lane == 0) red_add_release_sys(&g.pages[pend_owner]->rs_count[g.rank][pend_b], 1ull);
     }
     tc_fence_before_sync();
     cluster_sync_all();                                // nothing of the pair is in flight any more

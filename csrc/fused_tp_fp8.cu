@@ -354,6 +354,7 @@ gemm_rs_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const int quarter = warp % 4;
       int acc = 0;
       uint32_t acc_phase = 0;
+      int pend_owner = -1, pend_b = 0;                      // the tile whose stores were issued last
       for (int tile = cta; tile < num_tiles; tile += ctas) {
         const int tn = tile % tiles_n, rb = tile / tiles_n;
         const int owner = g.order[2 * rb], b = g.order[2 * rb + 1];
@@ -384,6 +385,9 @@ gemm_rs_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&p.acc_empty[acc]);      // the accumulator is free as soon as it sits in shared memory
+        // count the previous tile on its owner: its stores were issued a whole tile ago, so the release has nothing
+        // left to wait for (a release right behind the stores, let alone a system-scope fence, cost 8-30 us a tile)
+        if (pend_owner >= 0 && lane == 0) red_add_release_sys(&g.pages[pend_owner]->rs_count[g.rank][pend_b], 1ull);
         // two rows (256 contiguous bytes each) per store instruction, 16 rows in flight
         const int half = lane / 16, piece = lane % 16;
         char* dst0 = slab + ((static_cast<size_t>(b) * BM + quarter * 32 + half) * g.N + static_cast<size_t>(tn) * FBN) * 2 + piece * 16;
@@ -397,12 +401,12 @@ gemm_rs_mxfp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           for (int u = 0; u < 8; ++u) *reinterpret_cast<uint4*>(dst0 + static_cast<size_t>(r0 + 2 * u) * g.N * 2) = d[u];
         }
         __syncwarp();
-        if (lane == 0) {
-          __threadfence_system();
-          red_add_release_sys(&g.pages[owner]->rs_count[g.rank][b], 1ull);
-        }
+        pend_owner = owner;                                  // published while the next tile is staged (or after the loop)
+        pend_b = b;
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
+      // the last tile of this warp
+      if (pend_owner >= 0 && lane == 0) red_add_release_sys(&g.pages[pend_owner]->rs_count[g.rank][pend_b], 1ull);
     }
     tc_fence_before_sync();
     asm volatile("bar.sync 1, %0;" ::"r"(kGemmThreads) : "memory");

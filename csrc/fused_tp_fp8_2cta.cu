@@ -391,6 +391,7 @@ gemm_rs_mxfp8_2cta_kernel(const __grid_constant__ RsF8Maps maps, GemmRsF8Args g)
       const int quarter = warp % 4;
       uint32_t acc_phase = 0;
       uint8_t* epi = p.epi + (warp - 2) * kQEpiPerWarp;
+      int pend_owner = -1, pend_b = 0;                      // the tile whose stores were issued last
       for (int tile = cluster; tile < num_tiles; tile += pairs) {
         const int tn = tile % tiles_n, rb = 2 * (tile / tiles_n) + static_cast<int>(cta_rank);
         const int owner = g.order[2 * rb], b = g.order[2 * rb + 1];
@@ -401,6 +402,9 @@ gemm_rs_mxfp8_2cta_kernel(const __grid_constant__ RsF8Maps maps, GemmRsF8Args g)
           break;
         }
         tc_fence_after_sync();
+        // count the previous tile on its owner: its stores were issued a whole tile ago, so the release has nothing
+        // left to wait for (a release right behind the stores, let alone a system-scope fence, cost 8-30 us a tile)
+        if (pend_owner >= 0 && lane == 0) red_add_release_sys(&g.pages[pend_owner]->rs_count[g.rank][pend_b], 1ull);
         // destination: the owner's slab for source = me, local row inside the owner's shard
         char* slab = g.heap_bases[owner] + parity_off + static_cast<size_t>(g.rank) * slab_bytes;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -418,13 +422,12 @@ gemm_rs_mxfp8_2cta_kernel(const __grid_constant__ RsF8Maps maps, GemmRsF8Args g)
           store_staged_rows(epi, dst0, static_cast<size_t>(g.N) * 2, lane, 32);
           __syncwarp();
         }
-        // this quarter of the tile is on its way: make it visible on the owner, then count it there
-        if (lane == 0) {
-          __threadfence_system();
-          red_add_release_sys(&g.pages[owner]->rs_count[g.rank][b], 1ull);
-        }
+        pend_owner = owner;                                  // published while the next tile is staged (or after the loop)
+        pend_b = b;
         acc_phase ^= 1;
       }
+      // the last tile of this warp
+      if (pend_owner >= 0 && lane == 0) red_add_release_sys(&g.pages[pend_owner]->rs_count[g.rank][pend_b], 1ull);
     }
     tc_fence_before_sync();
     cluster_sync_all();                                // nothing of the pair is in flight any more

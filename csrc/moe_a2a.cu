@@ -272,7 +272,7 @@ moe_gemm_combine_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     // this warp's rows are on their way: tell every rank (one count per epilogue warp and CTA)
     __syncwarp();
     if (lane < g.nranks) {
-      __threadfence_system();
+      fence_acq_rel_sys();
       red_add_release_sys(&g.pages[lane]->moe_count[g.rank], 1ull);
     }
   }

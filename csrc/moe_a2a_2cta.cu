@@ -285,7 +285,7 @@ moe_gemm_combine_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __
     // this warp's rows are on their way: tell every rank (one count per epilogue warp and CTA)
     __syncwarp();
     if (!skip && lane < g.nranks) {
-      __threadfence_system();
+      fence_acq_rel_sys();
       red_add_release_sys(&g.pages[lane]->moe_count[g.rank], 1ull);
     }
   }

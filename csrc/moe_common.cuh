@@ -133,7 +133,7 @@ __device__ __forceinline__ void moe_comm_role(const MoeArgs& g, FusedPage* page,
     }
     __syncthreads();
     if (threadIdx.x < g.nranks) {
-      __threadfence_system();
+      fence_acq_rel_sys();
       st_release_sys(&g.pages[threadIdx.x]->moe_flag[g.rank][0], epoch);
     }
   }
@@ -175,10 +175,10 @@ __device__ __forceinline__ void moe_comm_role(const MoeArgs& g, FusedPage* page,
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-      __threadfence_system();
+      fence_acq_rel_sys();
       if (atomicAdd(&page->ag_block_count[0], 1u) == static_cast<unsigned int>(g.comm_ctas) - 1u) {
         page->ag_block_count[0] = 0;
-        __threadfence_system();
+        fence_acq_rel_sys();
         for (int q = 0; q < g.nranks; ++q) st_release_sys(&g.pages[(g.rank + q) % g.nranks]->moe_flag[g.rank][1], epoch);
       }
     }

@@ -15,6 +15,10 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
+// Release / acquire fence at system scope.  __threadfence_system() is the sequentially consistent fence (fence.sc.sys),
+// which costs several microseconds behind stores to a peer; the flag protocols here only need the ordering of a
+// release (the data before the flag) or an acquire (the flag before the data), which is what this fence gives.
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }

@@ -69,10 +69,10 @@ def register_b200_plans():
             # Two GPUs: the ring on two channels is the two-shot exchange with the receive, the reduction and the
             # send back fused into one step (three steps per threadblock instead of five).  Measured against NCCL
             # on the same box:
-            #   LL, 32 threadblocks      19.0 / 18.5 / 20.6 us at 64 KB / 256 KB / 1 MB    (NCCL 22.0 / 20.1 / 20.1)
-            #   LL128, 32 threadblocks   36.5 us at 4 MB                                    (NCCL 40.2; Simple 39.2)
-            #   Simple, 128 threadblocks 61 / 157 / 492 us at 16 / 64 / 256 MB              (NCCL 62 / 167 / 549)
-            for proto, low, high, inst in (('LL', '32KB', '2MB', 16), ('LL128', '2MB', '8MB', 16),
+            #   LL, 128 threadblocks      20.0 / 18.9 / 20.3 us at 64 KB / 256 KB / 1 MB   (NCCL 20.8 / 20.4 / 20.8)
+            #   LL128, 128 threadblocks   27.7 us at 4 MB                                   (NCCL 40.7; Simple 33.8; LL 33.4)
+            #   Simple, 128 threadblocks  61 / 157 / 492 us at 16 / 64 / 256 MB             (NCCL 62 / 167 / 549)
+            for proto, low, high, inst in (('LL', '32KB', '2MB', 64), ('LL128', '2MB', '8MB', 64),
                                            ('Simple', '8MB', None, reduce_copies[2] // 2)):
                 def ring(prog, nodes):
                     allreduce_ring(2, 2)
