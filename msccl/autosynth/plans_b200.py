@@ -25,8 +25,8 @@ def register_b200_plans():
     # The two-shot all-reduce has one threadblock per copy and peer and reduces locally between its two transfers:
     # 256 MB on two GPUs took 634 / 510 / 482 us with 32 / 64 / 128 copies (NCCL 526 us), on four GPUs 1132 / 918 us with
     # 16 / 32 copies (NCCL 682 us, which reduces inside the switch; so does the in-switch program of
-    # msccl.language.ext_nvls on registered tensors: 604 us).
-    reduce_copies = {2: 128, 4: 32, 8: 8}
+    # msccl.language.ext_nvls on registered tensors: 604 us); on eight GPUs 64 MB took 617 / 396 us with 8 / 16 copies.
+    reduce_copies = {2: 128, 4: 32, 8: 16}
     small = {2: 4, 4: 2, 8: 1}     # latency-bound sizes: flag-in-data packets, few CTAs
     # between the two: 128-byte lines with 120 bytes of payload (LL128), no fence per tile; ahead of the Simple plans up
     # to 1-2 MB on two GPUs (all-gather of 1 MB: 20.5 us against 22.1 us), behind them from 4 MB
@@ -58,13 +58,15 @@ def register_b200_plans():
                                    machines=lambda m: m == 1)(two_shot_ll128)
             # From 4 GPUs up the reduction belongs into the switch: the program of in-switch steps (one multimem
             # load-reduce and one multimem store per vector; `msccl.language.ext_nvls`) is what NCCL's NVLS algorithm
-            # does too, and no program of peer stores can match it (four GPUs, 64 MB: two-shot over peer stores 275 us,
-            # NCCL 188 us, in-switch program 170 us on registered tensors).  Tensors that are not registered memory
-            # pass through registered staging slices.
+            # does too, and no program of peer stores can match it.  Against NCCL on registered tensors: x1.1-1.8 from
+            # 64 KB to 256 MB on 8 GPUs, x0.8-0.9 below 1 MB and x1.1-2.3 above on 4 GPUs, where the two-shot program over
+            # peer stores reaches x0.4-0.75.  Tensors that are not registered memory pass through registered staging
+            # slices (8 GPUs: x1.4 at 16 MB, x0.98 at 256 MB).  The peer-store programs stay registered underneath for
+            # the sizes below.
             def in_switch(machines, n=n):
                 return allreduce_nvls(n, 8, name=f'b200_allreduce_in_switch_{n}')
             in_switch.__name__ = f'b200_allreduce_in_switch_{n}'
-            register_synthesis_plan('allreduce', mtype, machines=lambda m: m == 1, sizes=('4MB', None))(in_switch)
+            register_synthesis_plan('allreduce', mtype, machines=lambda m: m == 1, sizes=('64KB', None))(in_switch)
         else:
             # Two GPUs: the ring on two channels is the two-shot exchange with the receive, the reduction and the
             # send back fused into one step (three steps per threadblock instead of five).  Measured against NCCL

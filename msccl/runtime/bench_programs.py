@@ -64,7 +64,7 @@ def _allreduce_programs(n):
     from msccl.programs.allreduce import allreduce_one_shot, allreduce_ring, allreduce_two_shot
     from msccl.xml import load_xml
     manual = ThreadblockPolicy.manual
-    copies = {2: 128, 4: 32, 8: 8}.get(n, 8)
+    copies = {2: 128, 4: 32, 8: 16}.get(n, 8)
     ch = min(n, 4)
     return [
         # (program, smallest and largest message in bytes it is timed on)

@@ -281,7 +281,7 @@ class Executor:
     def _run_in_switch(self, plan, inputs, outputs, stream):
         """A program of in-switch steps (``msccl.language.ext_nvls``) on the native kernel of the same shape."""
         comm = self.comm
-        if comm.emulated_mode or not comm.mc_base:
+        if comm.emulated_mode or (not comm.mc_base and plan.nvls_kind != 'allreduce'):
             raise PlanError('in-switch programs need one process per GPU and a communicator with NVLink multicast')
         rank, world = comm.rank, comm.world
         t_in = inputs[rank]
@@ -297,8 +297,10 @@ class Executor:
         code = DTYPE_CODES[t_in.dtype]
         nat = comm.native
         if plan.nvls_kind == 'allreduce':
+            # without a multicast window the same two-shot all-reduce runs on peer loads and stores
             nat.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, offset, nbytes, code, rank, world, comm.dev_syncs,
-                                  comm.timeout_ns, 8, stream_h, pipelined=os.environ.get('MSCCL_TWOSHOT_PIPE', '0') == '1')
+                                  comm.timeout_ns, self._twoshot_ctas(nbytes), stream_h,
+                                  pipelined=bool(comm.mc_base) and os.environ.get('MSCCL_TWOSHOT_PIPE', '0') == '1')
             result = t_in
         elif plan.nvls_kind == 'allgather':            # in place: the own block already sits at its position
             block = nbytes // world
@@ -317,6 +319,12 @@ class Executor:
         self.launches += 1
         self.last_algorithm = f'in-switch {plan.nvls_kind}'
         return {rank: result}
+
+    def _twoshot_ctas(self, nbytes):
+        """CTAs of the two-shot kernel: the in-switch reduction is saturated by a few, peer loads want many in flight."""
+        if self.comm.mc_base:
+            return 8
+        return max(1, min(128, nbytes // (32 << 10) or 1))
 
     STAGE_SLICE_BYTES = 64 << 20
 
@@ -339,7 +347,7 @@ class Executor:
         main = stream or torch.cuda.current_stream()
         flat = tensor.view(-1).view(torch.uint8)
         code = DTYPE_CODES[tensor.dtype]
-        pipelined = os.environ.get('MSCCL_TWOSHOT_PIPE', '0') == '1'
+        pipelined = bool(comm.mc_base) and os.environ.get('MSCCL_TWOSHOT_PIPE', '0') == '1'
         if nbytes <= slice_bytes:
             if self.launches_staged:
                 main.wait_event(freed[0])                       # an earlier, sliced call may still copy out of slice 0
@@ -347,7 +355,7 @@ class Executor:
             with torch.cuda.stream(main):
                 stage.copy_(flat, non_blocking=True)
                 comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, base, nbytes, code, rank, world, comm.dev_syncs,
-                                              comm.timeout_ns, 8, main.cuda_stream, pipelined=pipelined)
+                                              comm.timeout_ns, self._twoshot_ctas(nbytes), main.cuda_stream, pipelined=pipelined)
                 flat.copy_(stage, non_blocking=True)
                 freed[0].record(main)
             self.launches += 1
@@ -369,7 +377,8 @@ class Executor:
                 loaded.record(s_in)
             main.wait_event(loaded)
             comm.native.twoshot_allreduce(comm.dev_heap_bases, comm.mc_base, base + half * slice_bytes, size, code, rank, world,
-                                          comm.dev_syncs, comm.timeout_ns, 8, main.cuda_stream, pipelined=pipelined)
+                                          comm.dev_syncs, comm.timeout_ns, self._twoshot_ctas(size), main.cuda_stream,
+                                          pipelined=pipelined)
             reduced = torch.cuda.Event()
             reduced.record(main)
             s_out.wait_event(reduced)

@@ -133,7 +133,10 @@ def test_in_switch_programs_go_to_the_native_kernels(ex):
         ex.run(ex.compile(allgather_nvls(n)), torch.zeros(n * 4096, dtype=torch.bfloat16), stream=s)
     plain = Executor(FakeComm(multicast=False))
     with pytest.raises(PlanError):
-        plain.run(plain.compile(allreduce_nvls(n)), plain.comm.symmetric(n * 4096, torch.bfloat16), stream=s)
+        plain.run(plain.compile(allgather_nvls(n)), plain.comm.symmetric(n * 4096, torch.bfloat16), stream=s)
+    # the all-reduce program still runs there: the same two-shot kernel on peer loads and stores (no multicast window)
+    plain.run(plain.compile(allreduce_nvls(n)), plain.comm.symmetric(n * 4096, torch.bfloat16), stream=s)
+    assert last(plain)[0] == 'twoshot_allreduce' and last(plain)[1][1] == 0
 
 
 def test_two_ranks_prefer_peer_loads_and_large_one_shot_blocks():

@@ -125,13 +125,12 @@ def test_init_environment(capsys, clean_env):
 def test_init_b200_plan_table(capsys, clean_env):
     msccl.init('b200', 1, ('allreduce', (0, None)), ('alltoall', '1MB'), ('allgather', '64KB'))
     out = capsys.readouterr().out
-    assert 'b200_allreduce_one_shot_8 with LL protocol' in out and 'b200_allreduce_two_shot_8' in out
-    assert 'b200_allreduce_two_shot_ll128_8 with LL128 protocol' in out          # 128-byte lines between the two
-    assert 'b200_alltoall_direct_ll128_8 with LL128 protocol' in out
+    assert 'b200_allreduce_one_shot_8 with LL protocol' in out
+    assert 'b200_allreduce_in_switch_8' in out                                     # from 64 KB: reduced inside the switch
+    assert 'b200_allreduce_two_shot' not in out                                    # the peer-store programs lose to it there
+    assert 'b200_alltoall_direct_ll128_8 with LL128 protocol' in out              # 128-byte lines between LL and Simple
     root = ET.parse(os.environ['MSCCL_CONFIG']).getroot()
-    assert 'b200_allreduce_in_switch_8' in out                                     # large messages: reduced inside the switch
-    assert root.tag == 'msccl_algos' and len(root.findall('load')) == 6
-    assert [e.get('proto') for e in root.findall('load')].count('LL128') == 2
+    assert root.tag == 'msccl_algos' and [e.get('proto') for e in root.findall('load')].count('LL128') == 1
     for entry in load_plan_table(os.environ['MSCCL_CONFIG']):
         assert validate(entry.algo) == [] and entry.algo.ngpus == 8
 
