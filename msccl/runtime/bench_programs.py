@@ -147,8 +147,8 @@ def _time_program(ex, comm, dist, plan, coll, dtype, lo, hi, rank, n, nccl_cache
         size = numel * esize
         iters = 20 if size <= (4 << 20) else 5
         for memory in ('ordinary', 'symmetric'):
-            if plan.nvls_kind is not None and memory == 'ordinary':
-                continue
+            if plan.nvls_kind is not None and memory == 'ordinary' and plan.nvls_kind != 'allreduce':
+                continue                     # only the in-switch all-reduce stages tensors that are not registered memory
             if coll == 'allreduce':
                 t = sym_a[:size].view(dtype) if memory == 'symmetric' else torch.zeros(numel, dtype=dtype, device='cuda')
                 fn = lambda: ex.run(plan, t)                                                 # noqa: E731
