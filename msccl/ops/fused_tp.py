@@ -30,7 +30,7 @@ class FusedTensorParallel:
         self.n = comm.world
         self.rows = tokens_per_rank
         self.hidden = hidden
-        self.comm_ctas = comm_ctas
+        self.comm_ctas = int(os.environ.get('MSCCL_COMM_CTAS', comm_ctas))      # CTAs that push the local shard to the peers
         all_rows = self.n * tokens_per_rank
         self.gathered_bytes = all_rows * hidden * 2
         _, self.gathered_off = comm.symmetric_empty(2 * all_rows * hidden, torch.bfloat16)
