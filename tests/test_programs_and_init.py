@@ -191,3 +191,23 @@ def test_every_registered_b200_plan_fits_the_executor(machine):
             assert plan.total_tbs() == len(algo.gpus[0].tbs)
             seen += 1
     assert seen >= 10
+
+
+def test_b200_allreduce_ranges_follow_the_measurements(capsys, clean_env):
+    # two GPUs: one-shot LL, then the two-channel ring in LL, LL128 and Simple; four GPUs: one-shot LL, then the in-switch program
+    msccl.init('b200x2', 1, ('allreduce', (0, None)))
+    out = capsys.readouterr().out
+    assert 'from 0 bytes to 32 KB is run b200_allreduce_one_shot_2 with LL protocol' in out
+    assert 'from 32 KB to 2 MB is run b200_allreduce_ring_2_ll with LL protocol' in out
+    assert 'from 2 MB to 8 MB is run b200_allreduce_ring_2_ll128 with LL128 protocol' in out
+    assert 'from 8 MB to infinity is run b200_allreduce_ring_2 with Simple protocol' in out
+    entries = load_plan_table(os.environ['MSCCL_CONFIG'])
+    ring = [e.algo for e in entries if e.algo.name.startswith('b200_allreduce_ring_2')]
+    assert len(ring) == 3 and all(len(a.gpus[0].tbs) == 128 and a.nchannels == 128 for a in ring)
+    msccl.init('b200x4', 1, ('allreduce', (0, None)))
+    out = capsys.readouterr().out
+    assert 'from 0 bytes to 64 KB is run b200_allreduce_one_shot_4 with LL protocol' in out
+    assert 'b200_allreduce_in_switch_4' in out and 'two_shot' not in out
+    from msccl.language.ext_nvls import classify
+    kinds = [classify(e.algo) for e in load_plan_table(os.environ['MSCCL_CONFIG'])]
+    assert kinds.count('allreduce') >= 1 and kinds[0] is None
