@@ -207,7 +207,7 @@ def run_ours(args):
     if path[0]:
         os.environ['MSCCL_CONFIG'] = path[0]
     arena = nbytes + (1 << 30) + (3 << 30) + (64 << 20)      # headline buffer, sweep output, fused TP / MoE buffers
-    ex = mt.init(arena_bytes=arena, fifo_bytes=256 << 20)
+    ex = mt.init(arena_bytes=arena, fifo_bytes=256 << 20, nccl_fallback=False)    # a refused call must fail here, not be timed on NCCL
     comm = mt.communicator()
     buf = mt.symmetric_empty(numel, dtype)
     pinned = (torch.randn(numel, dtype=torch.float32) * 0.01).to(dtype).pin_memory()

@@ -399,6 +399,8 @@ class Executor:
         if comm.emulated_mode:
             raise PlanError('collective entry points need one process per GPU; use run() with an emulated communicator')
         nbytes = tensor.numel() * tensor.element_size()
+        if tensor.dtype not in DTYPE_CODES:
+            raise PlanError(f'no reduction kernel for {tensor.dtype} (sums of fp32, bf16 and fp16 only)')
         stream_h = (stream or torch.cuda.current_stream()).cuda_stream
         code = DTYPE_CODES[tensor.dtype]
         if comm.world == 1:

@@ -106,6 +106,40 @@ def test_msccl_torch_needs_init():
         mt.all_reduce(torch.zeros(4))
 
 
+def test_msccl_torch_falls_back_to_the_library_when_a_call_is_refused(monkeypatch, capsys):
+    # a PlanError comes from host-side checks before any launch; the call then runs on torch.distributed, once announced
+    import torch.distributed as dist
+    import msccl.torch as mt
+    from msccl.runtime.plan import PlanError
+
+    class Refusing:
+        def all_reduce(self, t, stream=None):
+            raise PlanError('999 input elements are not divisible into 256 chunks')
+
+        def all_gather(self, out, inp, stream=None):
+            out.copy_(torch.cat([inp, inp]))                      # a call the executor can run is not redirected
+
+    calls = []
+    monkeypatch.setattr(dist, 'all_reduce', lambda t, group=None: calls.append(('all_reduce', t.numel(), group)))
+    monkeypatch.setattr(dist, 'all_gather_into_tensor', lambda o, i, group=None: calls.append(('all_gather', o.numel(), group)))
+    saved = dict(mt._state)
+    try:
+        mt._state.update(executor=Refusing(), comm=object(), group='grp', nccl_fallback=True, told=set())
+        x = torch.ones(999)
+        assert mt.all_reduce(x) is x and mt.all_reduce(x) is x
+        out = torch.zeros(8)
+        mt.all_gather_into_tensor(out, torch.arange(4.0))
+        assert calls == [('all_reduce', 999, 'grp'), ('all_reduce', 999, 'grp')] and out.tolist() == [0, 1, 2, 3, 0, 1, 2, 3]
+        said = capsys.readouterr().out
+        assert said.count('Falling back to NCCL baseline') == 1 and 'not divisible into 256 chunks' in said
+        mt._state.update(nccl_fallback=False)
+        with pytest.raises(PlanError):
+            mt.all_reduce(x)
+    finally:
+        mt._state.clear()
+        mt._state.update(saved)
+
+
 def test_route_top_k_renormalises():
     from msccl.ops.moe import route_top_k
     logits = torch.tensor([[0.0, 1.0, 2.0, 3.0], [5.0, 5.0, -9.0, -9.0]])
