@@ -183,7 +183,7 @@ def main(argv=None):
     from msccl.runtime import Communicator, Executor
     from msccl.xml.loader import load_plan_table
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument('--set', default='all', choices=['all', 'allreduce', 'synth', 'ndv4', 'registered'])
+    ap.add_argument('--set', default='all', help='all, or a comma-separated subset of allreduce, synth, ndv4, registered')
     ap.add_argument('--max-bytes', default='1GB')
     args = ap.parse_args(argv)
     if 'RANK' not in os.environ:
@@ -200,7 +200,10 @@ def main(argv=None):
     warm = torch.zeros(1024, device='cuda')
     dist.all_reduce(warm)                       # NCCL is up before any environment variable is touched below
     rows, nccl_cache = [], {}
-    sets = ['allreduce', 'synth', 'ndv4', 'registered'] if args.set == 'all' else [args.set]
+    known = ['allreduce', 'synth', 'ndv4', 'registered']
+    sets = known if args.set == 'all' else [v for v in args.set.split(',') if v]
+    if any(v not in known for v in sets):
+        raise SystemExit(f'--set takes "all" or a comma-separated subset of {", ".join(known)}')
 
     if 'allreduce' in sets:
         for algo, lo, hi in _allreduce_programs(n):
