@@ -320,7 +320,8 @@ def make_run(subparsers):
                                  'against the CPU interpreter and print one row per size')
         parser.add_argument('--trace', type=Path, default=None, metavar='FILE',
                             help='with --emulate: write per-step device time stamps of the last size to FILE (JSON rows: '
-                                 'rank, tb, step, type, start_ns, end_ns, wait_ns, move_ns)')
+                                 'rank, tb, step, type, start_ns, end_ns, wait_ns, move_ns, signal_ns; a FILE ending in .json '
+                                 'gets one Trace Event document for chrome://tracing / Perfetto instead)')
         parser.add_argument('--no-direct', action='store_true',
                             help='with --emulate: every tile through the FIFOs (no stores into the receivers\' buffers)')
 

@@ -291,8 +291,9 @@ def run_emulated(args):
         if args.trace is not None:
             ex.run(plan, ins, outs, direct=direct, trace=True)
             ex.check()
-            with open(args.trace, 'w') as f:
-                for rec in ex.last_trace():
-                    f.write(json.dumps(rec) + '\n')
+            from msccl.runtime import trace as step_trace
+            rows = ex.last_trace()
+            step_trace.write(rows, args.trace, algo.name)
+            print(json.dumps({'trace': str(args.trace), 'per_step_type': step_trace.summarize(rows)}), flush=True)
     finally:
         comm.close()

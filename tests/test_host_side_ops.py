@@ -282,3 +282,25 @@ def test_fused_kernel_order_tables_are_lowered_from_the_programs():
     assert g1 != g2 and g1[:4] == g2[:4] == [(2, b) for b in range(4)]
     # one rank: nothing moves
     assert fused_tp_tables(1, 4, 0) == ([0, 0, 0, 1, 0, 2, 0, 3], [0, 0, 0, 1, 0, 2, 0, 3], [0, 1, 2, 3])
+
+
+def test_step_trace_exports(tmp_path):
+    # the per-step records of the interpreter kernel as JSON lines, as a Trace Event document, and summed up per step type
+    import json
+    from msccl.runtime import trace
+    rows = [{'rank': 0, 'tb': 0, 'step': 0, 'type': 's', 'start_ns': 0, 'end_ns': 4000, 'wait_ns': 500, 'move_ns': 3000, 'signal_ns': 500},
+            {'rank': 0, 'tb': 1, 'step': 0, 'type': 'r', 'start_ns': 100, 'end_ns': 6100, 'wait_ns': 4000, 'move_ns': 2000, 'signal_ns': 0},
+            {'rank': 1, 'tb': 0, 'step': 1, 'type': 'r', 'start_ns': 200, 'end_ns': 2200, 'wait_ns': 1000, 'move_ns': 1000, 'signal_ns': 0}]
+    doc = trace.to_chrome_trace(rows, 'ring')
+    slices = [e for e in doc['traceEvents'] if e['ph'] == 'X']
+    names = [e for e in doc['traceEvents'] if e['ph'] == 'M']
+    assert len(slices) == 3 and slices[1]['name'] == '0: r' and slices[1]['ts'] == 0.1 and slices[1]['dur'] == 6.0
+    assert slices[1]['args'] == {'wait_us': 4.0, 'move_us': 2.0, 'signal_us': 0.0}
+    assert {(e['name'], e['pid'], e.get('tid')) for e in names} == {('process_name', 0, None), ('process_name', 1, None),
+                                                                    ('thread_name', 0, 0), ('thread_name', 0, 1), ('thread_name', 1, 0)}
+    assert trace.summarize(rows) == {'r': {'records': 2, 'wait_us': 2.5, 'move_us': 1.5, 'signal_us': 0.0},
+                                     's': {'records': 1, 'wait_us': 0.5, 'move_us': 3.0, 'signal_us': 0.5}}
+    trace.write(rows, tmp_path / 't.jsonl')
+    assert [json.loads(l) for l in open(tmp_path / 't.jsonl')] == rows
+    trace.write(rows, tmp_path / 't.json', 'ring')
+    assert json.load(open(tmp_path / 't.json'))['otherData'] == {'program': 'ring'}
