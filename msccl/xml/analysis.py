@@ -7,18 +7,22 @@ of its threadblocks send.  ``estimate_us`` turns that into a time with the two-p
 synthesis guide uses (reference ``examples/dgx1_allgather.ipynb`` cells 343-353: time = steps * alpha +
 size * rounds / chunks * beta), with alpha and beta taken from measurements of this executor instead of 1:
 
-    time = depth * alpha  +  max over GPUs ( bytes sent / min(port bandwidth, sending threadblocks * per-CTA rate) )
+    time = launch  +  depth * alpha  +  max over GPUs ( wire bytes sent / min(port bandwidth, sending threadblocks * per-CTA rate) )
 
-Defaults: alpha 2.5 us per step for Simple (flag wait plus system-scope fence) and 1.2 us for LL, 50 GB/s per
-threadblock, 770 GB/s per NVLink port and direction.  It is an estimate for choosing instance counts, not a
-measurement.
+Defaults, fitted to runs of the interpreter kernel on 2 B200: 11 us per launch (cooperative launch, the first flag
+round trip, the drain at the end), then per dependent step 5 us for Simple (flag wait plus system-scope fence; a ring of
+3 steps takes 29 us, a two-shot program of 5 steps 35 us at small sizes), 2.5 us for LL (3 steps: 19 us) and 3 us for
+LL128; 50 GB/s per threadblock, 770 GB/s per NVLink port and direction; LL moves 16 bytes per 8 bytes of payload,
+LL128 128 bytes per 120.  It is an estimate for choosing instance counts, not a measurement.
 """
 from collections import defaultdict, deque
 from dataclasses import dataclass, field
 
 from msccl.xml.loader import AlgoIR
 
-ALPHA_US = {'Simple': 2.5, 'LL': 1.2, 'LL128': 1.2}
+ALPHA_US = {'Simple': 5.0, 'LL': 2.5, 'LL128': 3.0}
+LAUNCH_US = 11.0
+WIRE_BYTES_PER_PAYLOAD_BYTE = {'Simple': 1.0, 'LL': 2.0, 'LL128': 128.0 / 120.0}
 CTA_GBS = 50.0
 PORT_GBS = 770.0
 
@@ -101,13 +105,13 @@ def estimate_us(algo: AlgoIR, nbytes: int, alpha_us=None, cta_gbs=CTA_GBS, port_
     """Estimated time in microseconds for a message of ``nbytes`` (the size the registry's ranges refer to:
     the input for all-reduce, reduce-scatter and all-to-all, the gathered output for all-gather)."""
     s = summary or summarize(algo)
-    alpha = ALPHA_US.get(algo.proto, 2.5) if alpha_us is None else alpha_us
+    alpha = ALPHA_US.get(algo.proto, ALPHA_US['Simple']) if alpha_us is None else alpha_us
     chunk_bytes = nbytes / chunks_per_message(algo)
-    wire = 2.0 if algo.proto in ('LL', 'LL128') else 1.0        # LL packets carry a flag per 8 bytes of data
+    wire = WIRE_BYTES_PER_PAYLOAD_BYTE.get(algo.proto, 1.0)     # flags travel with the data in LL and LL128
     slowest = 0.0
     for gpu, chunks in s.sent_chunks.items():
         if chunks == 0:
             continue
         rate = min(port_gbs, max(s.sending_tbs[gpu], 1) * cta_gbs)
         slowest = max(slowest, chunks * chunk_bytes * wire / (rate * 1e3))   # bytes / (GB/s) in us
-    return s.depth * alpha + slowest
+    return LAUNCH_US + s.depth * alpha + slowest

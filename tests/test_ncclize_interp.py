@@ -246,9 +246,12 @@ def test_program_summary_and_cost_estimate():
     assert s.complete and 2 * (n - 1) <= s.depth <= 2 * (n - 1) + 1
     assert set(s.sent_chunks.values()) == {2 * (n - 1)} and set(s.sending_tbs.values()) == {1}
     small, large = estimate_us(algo, 8 << 10, summary=s), estimate_us(algo, 1 << 30, summary=s)
-    assert abs(small - s.depth * 2.5) < 1.0                        # latency term dominates
+    assert abs(small - (11.0 + s.depth * 5.0)) < 1.0               # launch and per-step latency dominate
     bytes_out = 2 * (n - 1) / n * (1 << 30)
-    assert abs(large - (s.depth * 2.5 + bytes_out / 50e3)) < 1.0   # one sending threadblock at 50 GB/s
+    assert abs(large - (11.0 + s.depth * 5.0 + bytes_out / 50e3)) < 1.0   # one sending threadblock at 50 GB/s
+    # LL128 carries 120 bytes of payload per 128-byte line, LL 8 per 16
+    ll128 = load_xml(prog.generate_xml().replace('proto="Simple"', 'proto="LL128"'))
+    assert abs(estimate_us(ll128, 1 << 30) - (11.0 + s.depth * 3.0 + bytes_out * (128 / 120) / 50e3)) < 1.0
     # more instances: same depth, proportionally more sending threadblocks
     prog4 = MSCCLProgram('ring4', fully_connected(n), AllReduce(n, n, True), 4, threadblock_policy=ThreadblockPolicy.manual)
     with prog4:
